@@ -1,0 +1,497 @@
+// Split-KV decode attention over a slot-indexed bf16 KV pool that lives either in
+// host-pinned (mapped) memory or in HBM.
+//
+// Data layout: K and V pools are [n_slots, NH_kv, 128] bf16 (one 256-byte row per token and
+// head), the layout of the reference's token pool (directkv/directkv_pool.py:96-130) and, with
+// slot = row * row_stride + position, of its request pool (directkv/directkv_request_pool.py:66-76).
+//
+// Work decomposition: the past tokens of every (request, kv head) are cut into 16-token tiles;
+// all tiles of the batch form one linear sequence that is divided evenly over all warps of the
+// grid.  Each warp streams its tiles through a private ring of shared-memory stages filled by
+// TMA (one 3-D box of 16 rows x 256 B per K or V tile, straight from the pool - over PCIe when
+// the pool is host memory), keeps (m, l, O) of an online softmax in registers and writes one
+// fp32 partial per (request, kv head) piece it touched.  A merge kernel combines the partials
+// with the token decoded in this step (csrc/directKV_kernel.cuh:749-787 gives the algebra).
+//
+// Every wait is bounded; nothing traps.
+#pragma once
+
+#include "dkv_common.cuh"
+
+namespace dkv {
+
+constexpr int kHeadDim       = 128;
+constexpr int kTileTokens    = 16;                              // tokens per streamed tile
+constexpr int kRowBytes      = kHeadDim * 2;                    // one token, one head, bf16
+constexpr int kTileBytes     = kTileTokens * kRowBytes;         // 4096: K or V of one tile
+constexpr int kStageBytes    = 2 * kTileBytes;                  // K + V
+constexpr int kPartialStride = 132;                             // 128 O + m + l + 2 pad (fp32)
+
+struct AttnParams {
+    const __nv_bfloat16* q;        // query rows; row b starts at q + b * q_stride, then [NH_q, 128]
+    long long q_stride;            // elements between consecutive (virtual) requests
+    const int* page_table;         // [rows, pt_stride] page ids, or nullptr for contiguous rows
+    const int* row_map;            // [B] page-table / pool row of request b, or nullptr (row = b)
+    const int* seq_lens;           // [B] tokens attended by request b, INCLUDING n_new
+    const int* cum_tiles;          // [B + 1] exclusive prefix sum of past tiles (written by prep)
+    float* partials;               // [(total_warps + B * NH_kv * nsub), G, kPartialStride]
+    unsigned int* status;
+    int batch;
+    int nh_q, nh_kv;
+    int g_total;                   // NH_q / NH_kv
+    int nsub;                      // g_total / G: q-head sub-groups that re-read the same KV
+    int pt_stride;
+    int page_size, page_shift;     // power of two (paged mode)
+    int rows_per_box;              // min(16, page_size): rows one TMA box brings
+    long long row_stride;          // contiguous mode: slots per pool row
+    int n_new;                     // trailing tokens per request that are NOT read from the pool
+    int total_warps;               // gridDim.x * warps per CTA of the partial kernel
+    float scale_log2;              // softmax scale * log2(e)
+};
+
+// ---------------------------------------------------------------------------
+// prep: tiles per request -> exclusive prefix sum.  One CTA.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) attn_prep_kernel(const int* __restrict__ seq_lens, int batch, int n_new,
+                                                        int* __restrict__ cum_tiles) {
+    __shared__ int warp_tot[8];
+    __shared__ int carry_s;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) carry_s = 0;
+    __syncthreads();
+    for (int base = 0; base < batch; base += 256) {
+        const int b = base + tid;
+        int v = 0;
+        if (b < batch) {
+            int past = seq_lens[b] - n_new;
+            v = past > 0 ? (past + kTileTokens - 1) / kTileTokens : 0;
+        }
+        int x = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int y = __shfl_up_sync(0xffffffffu, x, o);
+            if (lane >= o) x += y;
+        }
+        if (lane == 31) warp_tot[warp] = x;
+        __syncthreads();
+        int woff = 0;
+        for (int w = 0; w < warp; ++w) woff += warp_tot[w];
+        const int carry = carry_s;
+        if (b < batch) cum_tiles[b] = carry + woff + x - v;
+        __syncthreads();
+        if (tid == 255) carry_s = carry + woff + x;
+        __syncthreads();
+    }
+    if (tid == 0) cum_tiles[batch] = carry_s;
+}
+
+// ---------------------------------------------------------------------------
+// Cursor over the linear tile sequence: (request b, head-slot hs = h * nsub + sub, tile).
+// ---------------------------------------------------------------------------
+struct TileCursor {
+    int b, hs, tile, tiles_b;
+    __device__ __forceinline__ void locate(const AttnParams& p, long long u, int nhs) {
+        int lo = 0, hi = p.batch - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (static_cast<long long>(p.cum_tiles[mid]) * nhs <= u) lo = mid; else hi = mid - 1;
+        }
+        b = lo;
+        tiles_b = p.cum_tiles[b + 1] - p.cum_tiles[b];
+        const long long r = u - static_cast<long long>(p.cum_tiles[b]) * nhs;
+        hs = tiles_b > 0 ? static_cast<int>(r / tiles_b) : 0;
+        tile = tiles_b > 0 ? static_cast<int>(r % tiles_b) : 0;
+    }
+    __device__ __forceinline__ void advance(const AttnParams& p, int nhs) {
+        if (++tile < tiles_b) return;
+        tile = 0;
+        if (++hs < nhs) return;
+        hs = 0;
+        do {
+            ++b;
+            tiles_b = b < p.batch ? p.cum_tiles[b + 1] - p.cum_tiles[b] : 1;
+        } while (b < p.batch && tiles_b == 0);
+    }
+};
+
+// Lane 0 only: start the TMA copies of one tile into a stage.
+__device__ __forceinline__ void issue_tile(const AttnParams& p, const CUtensorMap* tmK, const CUtensorMap* tmV,
+                                           const TileCursor& c, uint8_t* stage, uint64_t* bar) {
+    const int h = c.hs / p.nsub;
+    const int tok0 = c.tile * kTileTokens;
+    const int row = p.row_map ? p.row_map[c.b] : c.b;
+    if (p.page_table == nullptr) {
+        const long long slot0 = static_cast<long long>(row) * p.row_stride + tok0;
+        mbar_arrive_expect_tx(bar, kStageBytes);
+        tma_load_3d(stage, tmK, bar, 0, h, static_cast<int>(slot0));
+        tma_load_3d(stage + kTileBytes, tmV, bar, 0, h, static_cast<int>(slot0));
+    } else if (p.page_size >= kTileTokens) {
+        const int page = p.page_table[static_cast<long long>(row) * p.pt_stride + (tok0 >> p.page_shift)];
+        const long long slot0 = (static_cast<long long>(page) << p.page_shift) + (tok0 & (p.page_size - 1));
+        mbar_arrive_expect_tx(bar, kStageBytes);
+        tma_load_3d(stage, tmK, bar, 0, h, static_cast<int>(slot0));
+        tma_load_3d(stage + kTileBytes, tmV, bar, 0, h, static_cast<int>(slot0));
+    } else {
+        const int past = p.seq_lens[c.b] - p.n_new;
+        const int rows = p.rows_per_box;  // == page_size
+        int npages = (past - tok0 + rows - 1) >> p.page_shift;
+        const int max_pages = kTileTokens >> p.page_shift;
+        npages = npages < max_pages ? npages : max_pages;
+        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(npages * rows * kRowBytes * 2));
+        const int* pt = p.page_table + static_cast<long long>(row) * p.pt_stride + (tok0 >> p.page_shift);
+        for (int r = 0; r < npages; ++r) {
+            const long long slot0 = static_cast<long long>(pt[r]) << p.page_shift;
+            tma_load_3d(stage + r * rows * kRowBytes, tmK, bar, 0, h, static_cast<int>(slot0));
+            tma_load_3d(stage + kTileBytes + r * rows * kRowBytes, tmV, bar, 0, h, static_cast<int>(slot0));
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Partial attention.  Lane (g4 = lane / 8, j = lane % 8) owns tokens t == g4 (mod 4) of each
+// tile and the head-dim slices [8j, 8j+8) and [64+8j, 64+8j+8); a quarter-warp therefore reads
+// 128 contiguous bytes of a row with each 16-byte shared load (no bank conflicts).
+// ---------------------------------------------------------------------------
+template <int G, int NWARPS, int NST>
+__global__ void __launch_bounds__(NWARPS * 32, 1)
+attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const AttnParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g4 = lane >> 3, j = lane & 7;
+    uint8_t* wbase = smem + static_cast<size_t>(warp) * NST * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(NWARPS) * NST * kStageBytes) + warp * NST;
+
+    const int nhs = p.nh_kv * p.nsub;
+    const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
+    const long long qn = (U + p.total_warps - 1) / p.total_warps;
+    const int gw = blockIdx.x * NWARPS + warp;
+    const long long u0 = static_cast<long long>(gw) * qn;
+    const long long u1 = (u0 + qn < U) ? u0 + qn : U;
+    if (u0 >= u1) return;  // warps are independent: no CTA-wide barrier follows
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < NST; ++s) mbar_init(&bars[s], 1);
+        fence_mbar_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    __syncwarp();
+
+    TileCursor cc, pc;
+    cc.locate(p, u0, nhs);
+    pc = cc;
+    long long pu = u0;  // next unit the producer will issue
+
+    // Prologue: fill the ring.
+#pragma unroll
+    for (int s = 0; s < NST; ++s) {
+        if (pu < u1) {
+            if (lane == 0) issue_tile(p, &tmK, &tmV, pc, wbase + s * kStageBytes, &bars[s]);
+            pc.advance(p, nhs);
+            ++pu;
+        }
+    }
+
+    uint32_t phase_bits = 0;  // bit s = parity to wait for on stage s
+    int stage = 0;
+    bool failed = false;
+
+    float qf[G][16];
+    float O[G][16];
+    float m[G], l[G];
+    int past_b = 0;
+    bool seg_open = false;
+
+    for (long long u = u0; u < u1; ++u) {
+        if (!seg_open) {
+            // New (request, head-slot) piece: load and pre-scale its G query rows.
+            const int h = cc.hs / p.nsub, sub = cc.hs - h * p.nsub;
+            const __nv_bfloat16* qrow =
+                p.q + static_cast<long long>(cc.b) * p.q_stride + static_cast<long long>(h * p.g_total + sub * G) * kHeadDim;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const uint4 a = *reinterpret_cast<const uint4*>(qrow + g * kHeadDim + 8 * j);
+                const uint4 b2 = *reinterpret_cast<const uint4*>(qrow + g * kHeadDim + 64 + 8 * j);
+                const uint32_t w[8] = {a.x, a.y, a.z, a.w, b2.x, b2.y, b2.z, b2.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    qf[g][2 * i] = bf16lo(w[i]) * p.scale_log2;
+                    qf[g][2 * i + 1] = bf16hi(w[i]) * p.scale_log2;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) O[g][i] = 0.f;
+                m[g] = -INFINITY;
+                l[g] = 0.f;
+            }
+            past_b = p.seq_lens[cc.b] - p.n_new;
+            seg_open = true;
+        }
+
+        // ---- wait for this tile ----
+        // The vote keeps the decision warp-uniform: the shuffles below need every lane.
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bars[stage], (phase_bits >> stage) & 1u))) {
+            failed = true;
+            break;
+        }
+        phase_bits ^= (1u << stage);
+        const uint8_t* sK = wbase + stage * kStageBytes;
+        const uint8_t* sV = sK + kTileBytes;
+        const int valid = past_b - cc.tile * kTileTokens;  // >= 1; may exceed 16
+
+        // ---- S = q . k ----
+        float s[G][4];
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt) {
+            const int t = tt * 4 + g4;
+            const uint4 ka = *reinterpret_cast<const uint4*>(sK + t * kRowBytes + 16 * j);
+            const uint4 kb = *reinterpret_cast<const uint4*>(sK + t * kRowBytes + 128 + 16 * j);
+            const uint32_t w[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
+            float kf[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                kf[2 * i] = bf16lo(w[i]);
+                kf[2 * i + 1] = bf16hi(w[i]);
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    a0 = fmaf(qf[g][i], kf[i], a0);
+                    a1 = fmaf(qf[g][i + 1], kf[i + 1], a1);
+                }
+                float acc = a0 + a1;
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+                s[g][tt] = (t < valid) ? acc : -INFINITY;
+            }
+        }
+
+        // ---- online softmax (base-2 domain) ----
+        float pr[G][4];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float tm = fmaxf(fmaxf(s[g][0], s[g][1]), fmaxf(s[g][2], s[g][3]));
+            tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 8));
+            tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 16));
+            const float m_new = fmaxf(m[g], tm);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = exp2f(m[g] - m_use);  // m = -inf -> 0
+            float ps = 0.f;
+#pragma unroll
+            for (int tt = 0; tt < 4; ++tt) {
+                pr[g][tt] = exp2f(s[g][tt] - m_use);
+                ps += pr[g][tt];
+            }
+            l[g] = l[g] * alpha + ps;
+            m[g] = m_new;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) O[g][i] *= alpha;
+        }
+
+        // ---- O += P . V ----
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt) {
+            const int t = tt * 4 + g4;
+            if (t < valid) {
+                const uint4 va = *reinterpret_cast<const uint4*>(sV + t * kRowBytes + 16 * j);
+                const uint4 vb = *reinterpret_cast<const uint4*>(sV + t * kRowBytes + 128 + 16 * j);
+                const uint32_t w[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float v0 = bf16lo(w[i]), v1 = bf16hi(w[i]);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) {
+                        O[g][2 * i] = fmaf(pr[g][tt], v0, O[g][2 * i]);
+                        O[g][2 * i + 1] = fmaf(pr[g][tt], v1, O[g][2 * i + 1]);
+                    }
+                }
+            }
+        }
+        __syncwarp();  // every lane is done reading this stage
+
+        // ---- refill the stage ----
+        if (pu < u1) {
+            if (lane == 0) issue_tile(p, &tmK, &tmV, pc, wbase + stage * kStageBytes, &bars[stage]);
+            pc.advance(p, nhs);
+            ++pu;
+        }
+        stage = (stage + 1 == NST) ? 0 : stage + 1;
+
+        // ---- end of this (request, head-slot) piece? ----
+        const bool last_of_seg = (cc.tile + 1 == cc.tiles_b) || (u + 1 == u1);
+        if (last_of_seg) {
+            const int seg = cc.b * nhs + cc.hs;
+            float* out = p.partials + static_cast<size_t>(gw + seg) * (G * kPartialStride);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                float lt = l[g];
+                lt += __shfl_xor_sync(0xffffffffu, lt, 8);
+                lt += __shfl_xor_sync(0xffffffffu, lt, 16);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float o = O[g][i];
+                    o += __shfl_xor_sync(0xffffffffu, o, 8);
+                    o += __shfl_xor_sync(0xffffffffu, o, 16);
+                    O[g][i] = o;
+                }
+                if (g4 == 0) {
+                    float* og = out + g * kPartialStride;
+                    *reinterpret_cast<float4*>(og + 8 * j) = make_float4(O[g][0], O[g][1], O[g][2], O[g][3]);
+                    *reinterpret_cast<float4*>(og + 8 * j + 4) = make_float4(O[g][4], O[g][5], O[g][6], O[g][7]);
+                    *reinterpret_cast<float4*>(og + 64 + 8 * j) = make_float4(O[g][8], O[g][9], O[g][10], O[g][11]);
+                    *reinterpret_cast<float4*>(og + 64 + 8 * j + 4) =
+                        make_float4(O[g][12], O[g][13], O[g][14], O[g][15]);
+                    if (j == 0) {
+                        og[128] = m[g];
+                        og[129] = lt;
+                    }
+                }
+            }
+            seg_open = false;
+        }
+        cc.advance(p, nhs);
+    }
+
+    if (failed) {
+        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+        // Give copies still in flight a bounded chance to land before the stages are released.
+        for (int s = 0; s < NST; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Merge: one warp per (request, q head); lane owns head-dim elements [4 lane, 4 lane + 4).
+// Combines the partials of every warp that touched the (request, kv head) piece with the
+// token decoded in this step (its K/V come from the projection kernel or from the caller).
+// Output modes: normalised bf16 rows, and/or the unnormalised fp32 (O, m, l) triple used when
+// the sequence is split across GPUs.
+// ---------------------------------------------------------------------------
+struct MergeParams {
+    AttnParams a;
+    int G;                           // q heads per partial record (template G of the partial kernel)
+    const __nv_bfloat16* kv_new;     // [B, NH_kv, 2, 128] bf16 or nullptr (n_new == 0)
+    __nv_bfloat16* out;              // [B, NH_q, 128] bf16 (row b at out + b * out_stride) or nullptr
+    long long out_stride;
+    float* lse;                      // [B, NH_q] natural-log LSE, or nullptr
+    float* part_out;                 // [B, NH_q, kPartialStride] unnormalised partial, or nullptr
+};
+
+__global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams mp) {
+    const AttnParams& p = mp.a;
+    const int lane = threadIdx.x & 31;
+    const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (wid >= static_cast<long long>(p.batch) * p.nh_q) return;
+    const int b = static_cast<int>(wid / p.nh_q), hq = static_cast<int>(wid % p.nh_q);
+    const int h = hq / p.g_total, gt = hq % p.g_total;
+    const int sub = gt / mp.G, g = gt % mp.G;
+    const int nhs = p.nh_kv * p.nsub;
+    const int hs = h * p.nsub + sub;
+
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float m = -INFINITY, l = 0.f;
+
+    const int tiles_b = p.cum_tiles[b + 1] - p.cum_tiles[b];
+    if (tiles_b > 0) {
+        const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
+        const long long qn = (U + p.total_warps - 1) / p.total_warps;
+        const long long s0 = static_cast<long long>(p.cum_tiles[b]) * nhs + static_cast<long long>(hs) * tiles_b;
+        const long long e0 = s0 + tiles_b;
+        const int seg = b * nhs + hs;
+        const int gw_first = static_cast<int>(s0 / qn), gw_last = static_cast<int>((e0 - 1) / qn);
+        for (int gw = gw_first; gw <= gw_last; ++gw) {
+            const float* rec = p.partials + static_cast<size_t>(gw + seg) * (mp.G * kPartialStride) + g * kPartialStride;
+            const float mi = rec[128], li = rec[129];
+            const float4 oi = *reinterpret_cast<const float4*>(rec + 4 * lane);
+            const float mn = fmaxf(m, mi);
+            const float mu = (mn == -INFINITY) ? 0.f : mn;
+            const float a = exp2f(m - mu), c = exp2f(mi - mu);
+            acc.x = acc.x * a + oi.x * c;
+            acc.y = acc.y * a + oi.y * c;
+            acc.z = acc.z * a + oi.z * c;
+            acc.w = acc.w * a + oi.w * c;
+            l = l * a + li * c;
+            m = mn;
+        }
+    }
+
+    const __nv_bfloat16* qrow = p.q + static_cast<long long>(b) * p.q_stride + static_cast<long long>(hq) * kHeadDim;
+    if (mp.kv_new != nullptr && p.n_new > 0) {
+        const __nv_bfloat16* kn = mp.kv_new + (static_cast<long long>(b) * p.nh_kv + h) * 2 * kHeadDim;
+        const uint2 qw = *reinterpret_cast<const uint2*>(qrow + 4 * lane);
+        const uint2 kw = *reinterpret_cast<const uint2*>(kn + 4 * lane);
+        float d = bf16lo(qw.x) * bf16lo(kw.x) + bf16hi(qw.x) * bf16hi(kw.x) + bf16lo(qw.y) * bf16lo(kw.y) +
+                  bf16hi(qw.y) * bf16hi(kw.y);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        const float sn = d * p.scale_log2;
+        const uint2 vw = *reinterpret_cast<const uint2*>(kn + kHeadDim + 4 * lane);
+        const float mn = fmaxf(m, sn);
+        const float a = exp2f(m - mn), c = exp2f(sn - mn);
+        acc.x = acc.x * a + bf16lo(vw.x) * c;
+        acc.y = acc.y * a + bf16hi(vw.x) * c;
+        acc.z = acc.z * a + bf16lo(vw.y) * c;
+        acc.w = acc.w * a + bf16hi(vw.y) * c;
+        l = l * a + c;
+        m = mn;
+    }
+
+    if (mp.part_out != nullptr) {
+        float* po = mp.part_out + (static_cast<long long>(b) * p.nh_q + hq) * kPartialStride;
+        *reinterpret_cast<float4*>(po + 4 * lane) = acc;
+        if (lane == 0) {
+            po[128] = m;
+            po[129] = l;
+        }
+    }
+    if (mp.out != nullptr) {
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        uint2 w;
+        w.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+        w.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(mp.out + static_cast<long long>(b) * mp.out_stride +
+                                  static_cast<long long>(hq) * kHeadDim + 4 * lane) = w;
+    }
+    if (mp.lse != nullptr && lane == 0)
+        mp.lse[static_cast<long long>(b) * p.nh_q + hq] = (l > 0.f) ? m * 0.6931471805599453f + logf(l) : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------
+// Merge of R unnormalised partial sets [R, rows, kPartialStride] (sequence split across GPUs,
+// after the all-gather): one warp per row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) merge_rank_partials_kernel(const float* __restrict__ parts, int nranks,
+                                                                  long long rows, __nv_bfloat16* __restrict__ out,
+                                                                  float* __restrict__ lse) {
+    const int lane = threadIdx.x & 31;
+    const long long r = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float m = -INFINITY, l = 0.f;
+    for (int k = 0; k < nranks; ++k) {
+        const float* rec = parts + (static_cast<long long>(k) * rows + r) * kPartialStride;
+        const float mi = rec[128], li = rec[129];
+        const float4 oi = *reinterpret_cast<const float4*>(rec + 4 * lane);
+        const float mn = fmaxf(m, mi);
+        const float mu = (mn == -INFINITY) ? 0.f : mn;
+        const float a = exp2f(m - mu), c = exp2f(mi - mu);
+        acc.x = acc.x * a + oi.x * c;
+        acc.y = acc.y * a + oi.y * c;
+        acc.z = acc.z * a + oi.z * c;
+        acc.w = acc.w * a + oi.w * c;
+        l = l * a + li * c;
+        m = mn;
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    uint2 w;
+    w.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+    w.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(out + r * kHeadDim + 4 * lane) = w;
+    if (lse != nullptr && lane == 0) lse[r] = (l > 0.f) ? m * 0.6931471805599453f + logf(l) : -INFINITY;
+}
+
+}  // namespace dkv

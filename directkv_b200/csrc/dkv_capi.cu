@@ -1,0 +1,829 @@
+// C ABI of the engine (see include/directkv_b200.h): context, per-layer TMA descriptors,
+// scratch management, argument checks and kernel launches.  Built with nvcc for sm_100a into
+// libdirectkv_b200.so; depends only on the CUDA runtime (the one driver entry point it needs,
+// cuTensorMapEncodeTiled, is looked up at run time so the library loads on a machine
+// without a GPU driver).
+#include "../../include/directkv_b200.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+
+#include "dkv_attn.cuh"
+#include "dkv_proj.cuh"
+
+namespace {
+
+using namespace dkv;
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define DKV_CUDA(expr)                                                                              \
+    do {                                                                                            \
+        cudaError_t _e = (expr);                                                                    \
+        if (_e != cudaSuccess)                                                                      \
+            return fail(DKV_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+    } while (0)
+
+#define DKV_REQUIRE(cond, ...)                           \
+    do {                                                 \
+        if (!(cond)) return fail(DKV_ERR_INVALID, __VA_ARGS__); \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// KV pool [n_slots, nh, 128] bf16 as a 3-D map (d, head, slot); one box = `rows` token rows of one head.
+int encode_pool_map(CUtensorMap* m, void* base, int64_t n_slots, int nh, int rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return fail(DKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t gdim[3] = {128, (cuuint64_t)nh, (cuuint64_t)n_slots};
+    cuuint64_t gstr[2] = {256, (cuuint64_t)nh * 256};
+    cuuint32_t box[3] = {128, 1, (cuuint32_t)rows};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DKV_ERR_CUDA, "cuTensorMapEncodeTiled(pool) failed: %d", (int)r);
+    return DKV_OK;
+}
+
+// Row-major [rows, cols] bf16 matrix as a 2-D map; box = 128 rows x 64 columns, 128-byte swizzle.
+int encode_operand_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return fail(DKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t gstr[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DKV_ERR_CUDA, "cuTensorMapEncodeTiled(operand) failed: %d", (int)r);
+    return DKV_OK;
+}
+
+struct LayerState {
+    dkv_layer_desc d{};
+    void* k_dev = nullptr;  // device-visible address of the pool
+    void* v_dev = nullptr;
+    CUtensorMap tmK_page{}, tmV_page{};  // box rows = min(16, page_size)
+    CUtensorMap tmK_16{}, tmV_16{};      // box rows = 16 (contiguous rows)
+    CUtensorMap tmWk{}, tmWv{};
+    int page_shift = 0;
+    int rows_per_box = 16;
+    bool has_weights = false;
+};
+
+constexpr int kMaxCounters = 4096;
+
+}  // namespace
+
+struct dkv_context {
+    int device = 0;
+    int sm_count = 0;
+    uint8_t* scratch = nullptr;
+    size_t scratch_bytes = 0;
+    unsigned int* status = nullptr;     // device status word
+    unsigned int* counters = nullptr;   // split-K arrival counters, zero between launches
+    std::map<int, LayerState> layers;
+    int attn_variant = 0;
+    int attn_ctas = 0;
+    int proj_split_k = 0;
+};
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// Small kernels that live with the host logic
+// ---------------------------------------------------------------------------
+
+// Decode: position and destination slot of the token each request adds in this step.
+__global__ void decode_newtok_kernel(const int* __restrict__ seq_lens, const int* __restrict__ page_table,
+                                     int pt_stride, const int* __restrict__ row_map, int batch, int page_size,
+                                     int page_shift, long long row_stride, int save, int* __restrict__ tok_pos,
+                                     int* __restrict__ tok_slot) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= batch) return;
+    const int pos = seq_lens[b] - 1;
+    tok_pos[b] = pos;
+    long long slot = -1;
+    if (save && pos >= 0) {
+        const int row = row_map ? row_map[b] : b;
+        if (page_table)
+            slot = (static_cast<long long>(page_table[static_cast<long long>(row) * pt_stride + (pos >> page_shift)])
+                    << page_shift) + (pos & (page_size - 1));
+        else
+            slot = static_cast<long long>(row) * row_stride + pos;
+    }
+    tok_slot[b] = static_cast<int>(slot);
+}
+
+// Extend: every new row becomes a virtual request that attends past + its causal prefix.
+__global__ void extend_prep_kernel(int B, int S_new, int seqlen_past_host, const int* __restrict__ n_past_blocks_dev,
+                                   int is_causal, const int* __restrict__ row_map, long long row_stride,
+                                   int* __restrict__ vseq, int* __restrict__ vrow, int* __restrict__ tok_pos,
+                                   int* __restrict__ tok_slot) {
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= B * S_new) return;
+    const int b = v / S_new, i = v - b * S_new;
+    const int past = n_past_blocks_dev ? n_past_blocks_dev[0] * 64 : seqlen_past_host;
+    const int row = row_map ? row_map[b] : b;
+    vseq[v] = is_causal ? past + i + 1 : past + S_new;
+    vrow[v] = row;
+    tok_pos[v] = past + i;
+    tok_slot[v] = static_cast<int>(static_cast<long long>(row) * row_stride + past + i);
+}
+
+// DKV_NEW_GIVEN: pack the caller's K/V rows into kv_new [B, nh, 2, 128] and store them to the pool.
+__global__ void store_new_kv_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+                                    int batch, int nh, const int* __restrict__ tok_slot, __nv_bfloat16* k_pool,
+                                    __nv_bfloat16* v_pool, long long n_slots, __nv_bfloat16* __restrict__ kv_new,
+                                    unsigned int* status) {
+    const int lane = threadIdx.x & 31;
+    const long long w = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (w >= static_cast<long long>(batch) * nh) return;
+    const int b = static_cast<int>(w / nh), h = static_cast<int>(w % nh);
+    const __nv_bfloat16* src = (lane < 16 ? k_new : v_new) + (static_cast<long long>(b) * nh + h) * 128 + (lane & 15) * 8;
+    const uint4 val = *reinterpret_cast<const uint4*>(src);
+    *reinterpret_cast<uint4*>(kv_new + (static_cast<long long>(b) * nh + h) * 256 + lane * 8) = val;
+    const long long slot = tok_slot[b];
+    if (slot >= 0) {
+        if (slot < n_slots) {
+            __nv_bfloat16* dst = (lane < 16 ? k_pool : v_pool) + (slot * nh + h) * 128 + (lane & 15) * 8;
+            *reinterpret_cast<uint4*>(dst) = val;
+        } else if (lane == 0) {
+            atomicOr(status, kStatusBadSlot);
+        }
+    }
+}
+
+// Optional Neox rotation of Q rows at positions q_pos_start + i (csrc/directKV_kernel.cuh:619-638).
+__global__ void rope_q_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ q_rot, int B, int S_new,
+                              int nh_q, const float* __restrict__ cos_sin, int max_pos, int q_pos_start,
+                              unsigned int* status) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long total = static_cast<long long>(B) * S_new * nh_q * 64;
+    if (idx >= total) return;
+    const int d = static_cast<int>(idx & 63);
+    const long long rh = idx >> 6;  // (b, i, head)
+    const int i = static_cast<int>((rh / nh_q) % S_new);
+    const int pos = q_pos_start + i;
+    const float lo = __bfloat162float(q[rh * 128 + d]), hi = __bfloat162float(q[rh * 128 + 64 + d]);
+    float c = 1.f, s = 0.f;
+    if (pos >= 0 && pos < max_pos) {
+        c = cos_sin[static_cast<long long>(pos) * 128 + d];
+        s = cos_sin[static_cast<long long>(pos) * 128 + 64 + d];
+    } else {
+        atomicOr(status, kStatusBadPosition);
+    }
+    q_rot[rh * 128 + d] = __float2bfloat16_rn(lo * c - hi * s);
+    q_rot[rh * 128 + 64 + d] = __float2bfloat16_rn(hi * c + lo * s);
+}
+
+// Token-pool store: row i of src [n, row_bytes] goes to slot loc[i] of dst [n_slots, row_bytes].
+// One CTA per token; 16-byte stores (row_bytes is a multiple of 16).
+template <typename IndexT>
+__global__ void __launch_bounds__(128) scatter_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                                           const IndexT* __restrict__ loc, long long n_slots,
+                                                           int row_vec, unsigned int* status) {
+    const long long i = blockIdx.x;
+    const long long slot = static_cast<long long>(loc[i]);
+    if (slot < 0 || slot >= n_slots) {
+        if (threadIdx.x == 0) atomicOr(status, kStatusBadSlot);
+        return;
+    }
+    for (int c = threadIdx.x; c < row_vec; c += blockDim.x) dst[slot * row_vec + c] = src[i * row_vec + c];
+}
+
+// Plain streaming copy (16-byte read-only loads), for measuring what SM-issued reads of
+// host-mapped memory reach on this machine's host link.
+__global__ void __launch_bounds__(256) stream_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                                          long long n16) {
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16; i += stride)
+        dst[i] = __ldg(src + i);
+}
+
+// ---------------------------------------------------------------------------
+// Launch helpers
+// ---------------------------------------------------------------------------
+template <int G, int NW, int NST>
+constexpr size_t attn_smem_bytes() {
+    return static_cast<size_t>(NW) * NST * kStageBytes + static_cast<size_t>(NW) * NST * 8;
+}
+
+template <int G, int NW, int NST>
+cudaError_t attn_set_attr() {
+    return cudaFuncSetAttribute(attn_partial_kernel<G, NW, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(attn_smem_bytes<G, NW, NST>()));
+}
+
+template <int G, int NW, int NST>
+cudaError_t attn_launch(int ctas, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p,
+                        cudaStream_t st) {
+    attn_partial_kernel<G, NW, NST><<<ctas, NW * 32, attn_smem_bytes<G, NW, NST>(), st>>>(tmK, tmV, p);
+    return cudaGetLastError();
+}
+
+// Warps per CTA of the selectable variants of the streaming kernel (stages: 3, 2, 1).
+constexpr int kVarWarps[3] = {8, 12, 16};
+
+template <int G>
+cudaError_t attn_dispatch(int variant, int ctas, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p,
+                          cudaStream_t st) {
+    switch (variant) {
+        case 1: return attn_launch<G, 12, 2>(ctas, tmK, tmV, p, st);
+        case 2: if (G <= 2) return attn_launch<(G <= 2 ? G : 1), 16, 1>(ctas, tmK, tmV, p, st);
+                return attn_launch<G, 12, 2>(ctas, tmK, tmV, p, st);
+        default: return attn_launch<G, 8, 3>(ctas, tmK, tmV, p, st);
+    }
+}
+
+constexpr int kProjStages = 4;
+constexpr size_t kProjSmem = static_cast<size_t>(kProjStages) * kProjStage + 1024 /*control*/ + 1024 /*alignment*/;
+
+size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+struct ScratchPlan {
+    size_t cum, tok_pos, tok_slot, vseq, vrow, partials, kv_new, splitk, q_rot, total;
+};
+
+int choose_g(int g_total) { return (g_total % 4 == 0) ? 4 : (g_total % 2 == 0) ? 2 : 1; }
+
+int variant_warps(const dkv_context* ctx, int G) {
+    int v = ctx->attn_variant;
+    if (v == 2 && G > 2) v = 1;
+    return kVarWarps[v];
+}
+
+int attn_cta_count(const dkv_context* ctx) { return ctx->attn_ctas > 0 ? ctx->attn_ctas : ctx->sm_count; }
+
+void proj_split(const dkv_context* ctx, int T, int nh_kv, int H, int* split_k, int* cps) {
+    const int tiles = ((T + kProjBM - 1) / kProjBM) * nh_kv;
+    const int nchunks = H / kProjBK;
+    int s = ctx->proj_split_k > 0 ? ctx->proj_split_k : ctx->sm_count / (tiles > 0 ? tiles : 1);
+    if (s < 1) s = 1;
+    if (s > nchunks) s = nchunks;
+    if (tiles > kMaxCounters) s = 1;
+    const int c = (nchunks + s - 1) / s;
+    *cps = c;
+    *split_k = (nchunks + c - 1) / c;  // no empty slice
+}
+
+ScratchPlan plan_scratch(const dkv_context* ctx, int64_t rows, int nh_q, int nh_kv, int hidden, bool with_proj,
+                         bool with_qrot) {
+    ScratchPlan s{};
+    const int g_total = nh_q / nh_kv;
+    const int G = choose_g(g_total);
+    const int nsub = g_total / G;
+    const size_t total_warps = static_cast<size_t>(attn_cta_count(ctx)) * 16;  // upper bound over variants
+    size_t off = 0;
+    s.cum = off;      off += align256((rows + 1) * 4);
+    s.tok_pos = off;  off += align256(rows * 4);
+    s.tok_slot = off; off += align256(rows * 4);
+    s.vseq = off;     off += align256(rows * 4);
+    s.vrow = off;     off += align256(rows * 4);
+    s.partials = off; off += align256((total_warps + static_cast<size_t>(rows) * nh_kv * nsub) * G * kPartialStride * 4);
+    s.kv_new = off;   off += align256(static_cast<size_t>(rows) * nh_kv * 256 * 2);
+    s.splitk = off;
+    if (with_proj && hidden > 0) {
+        int split_k, cps;
+        proj_split(ctx, static_cast<int>(rows), nh_kv, hidden, &split_k, &cps);
+        if (split_k > 1) {
+            const size_t tiles = static_cast<size_t>((rows + kProjBM - 1) / kProjBM) * nh_kv;
+            off += align256(static_cast<size_t>(split_k) * tiles * kProjBM * kProjBN * 4);
+        }
+    }
+    s.q_rot = off;
+    if (with_qrot) off += align256(static_cast<size_t>(rows) * nh_q * 128 * 2);
+    s.total = off;
+    return s;
+}
+
+int ensure_scratch(dkv_context* ctx, size_t bytes) {
+    if (bytes <= ctx->scratch_bytes) return DKV_OK;
+    uint8_t* p = nullptr;
+    const size_t want = bytes + (bytes >> 2);
+    DKV_CUDA(cudaMalloc(&p, want));
+    if (ctx->scratch) {
+        DKV_CUDA(cudaDeviceSynchronize());
+        DKV_CUDA(cudaFree(ctx->scratch));
+    }
+    ctx->scratch = p;
+    ctx->scratch_bytes = want;
+    return DKV_OK;
+}
+
+int device_pointer_of(void* p, void** out, const char* what) {
+    cudaPointerAttributes attr;
+    DKV_CUDA(cudaPointerGetAttributes(&attr, p));
+    if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) {
+        *out = p;
+        return DKV_OK;
+    }
+    if (attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr) {
+        *out = attr.devicePointer;
+        return DKV_OK;
+    }
+    return fail(DKV_ERR_INVALID, "%s must be pinned (page-locked) host memory or device memory", what);
+}
+
+int build_layer(LayerState* L, const dkv_layer_desc* d) {
+    DKV_REQUIRE(d->k_pool && d->v_pool, "k_pool / v_pool must not be NULL");
+    DKV_REQUIRE(d->n_slots > 0 && d->nh_kv > 0, "n_slots and nh_kv must be positive");
+    DKV_REQUIRE(d->page_size >= 1 && (d->page_size & (d->page_size - 1)) == 0, "page_size (%d) must be a power of two",
+                d->page_size);
+    DKV_REQUIRE((reinterpret_cast<uintptr_t>(d->k_pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(d->v_pool) & 15) == 0,
+                "KV pool base addresses must be 16-byte aligned");
+    L->d = *d;
+    int rc;
+    if ((rc = device_pointer_of(d->k_pool, &L->k_dev, "k_pool")) != DKV_OK) return rc;
+    if ((rc = device_pointer_of(d->v_pool, &L->v_dev, "v_pool")) != DKV_OK) return rc;
+    L->page_shift = 0;
+    while ((1 << L->page_shift) < d->page_size) ++L->page_shift;
+    L->rows_per_box = d->page_size < kTileTokens ? d->page_size : kTileTokens;
+    if ((rc = encode_pool_map(&L->tmK_page, L->k_dev, d->n_slots, d->nh_kv, L->rows_per_box)) != DKV_OK) return rc;
+    if ((rc = encode_pool_map(&L->tmV_page, L->v_dev, d->n_slots, d->nh_kv, L->rows_per_box)) != DKV_OK) return rc;
+    if ((rc = encode_pool_map(&L->tmK_16, L->k_dev, d->n_slots, d->nh_kv, kTileTokens)) != DKV_OK) return rc;
+    if ((rc = encode_pool_map(&L->tmV_16, L->v_dev, d->n_slots, d->nh_kv, kTileTokens)) != DKV_OK) return rc;
+    L->has_weights = (d->wk != nullptr && d->wv != nullptr);
+    if (L->has_weights) {
+        DKV_REQUIRE(d->hidden > 0 && d->hidden % kProjBK == 0, "hidden (%d) must be a positive multiple of 64", d->hidden);
+        if ((rc = encode_operand_map(&L->tmWk, d->wk, static_cast<int64_t>(d->nh_kv) * 128, d->hidden)) != DKV_OK) return rc;
+        if ((rc = encode_operand_map(&L->tmWv, d->wv, static_cast<int64_t>(d->nh_kv) * 128, d->hidden)) != DKV_OK) return rc;
+    }
+    if (d->cos_sin) DKV_REQUIRE(d->max_pos > 0, "max_pos must be positive when cos_sin is given");
+    return DKV_OK;
+}
+
+// Projection of T rows of X with RoPE and write-back (tcgen05 kernel).
+int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int T, const int* tok_pos,
+                      const int* tok_slot, bool store_pool, __nv_bfloat16* kv_new, float* splitk, cudaStream_t st) {
+    CUtensorMap tmX;
+    int rc = encode_operand_map(&tmX, x, T, L.d.hidden);
+    if (rc != DKV_OK) return rc;
+    ProjParams pp{};
+    pp.T = T;
+    pp.H = L.d.hidden;
+    pp.nh_kv = L.d.nh_kv;
+    proj_split(ctx, T, L.d.nh_kv, L.d.hidden, &pp.split_k, &pp.chunks_per_split);
+    pp.tok_pos = tok_pos;
+    pp.tok_slot = tok_slot;
+    pp.cos_sin = L.d.cos_sin;
+    pp.max_pos = L.d.max_pos;
+    pp.k_pool = store_pool ? static_cast<__nv_bfloat16*>(L.k_dev) : nullptr;
+    pp.v_pool = store_pool ? static_cast<__nv_bfloat16*>(L.v_dev) : nullptr;
+    pp.n_slots = L.d.n_slots;
+    pp.kv_new = kv_new;
+    pp.splitk_scratch = splitk;
+    pp.tile_counters = ctx->counters;
+    pp.status = ctx->status;
+    dim3 grid(L.d.nh_kv, (T + kProjBM - 1) / kProjBM, pp.split_k);
+    proj_rope_kernel<kProjStages><<<grid, 128, kProjSmem, st>>>(tmX, L.tmWk, L.tmWv, pp);
+    DKV_CUDA(cudaGetLastError());
+    return DKV_OK;
+}
+
+int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool paged, const MergeParams& mp_in,
+                     cudaStream_t st) {
+    const int G = choose_g(ap.g_total);
+    ap.nsub = ap.g_total / G;
+    const int ctas = attn_cta_count(ctx);
+    ap.total_warps = ctas * variant_warps(ctx, G);
+    const CUtensorMap& tmK = paged ? L.tmK_page : L.tmK_16;
+    const CUtensorMap& tmV = paged ? L.tmV_page : L.tmV_16;
+    cudaError_t e;
+    if (G == 4) e = attn_dispatch<4>(ctx->attn_variant, ctas, tmK, tmV, ap, st);
+    else if (G == 2) e = attn_dispatch<2>(ctx->attn_variant, ctas, tmK, tmV, ap, st);
+    else e = attn_dispatch<1>(ctx->attn_variant, ctas, tmK, tmV, ap, st);
+    DKV_CUDA(e);
+    MergeParams mp = mp_in;
+    mp.a = ap;
+    mp.G = G;
+    const long long warps = static_cast<long long>(ap.batch) * ap.nh_q;
+    const int blocks = static_cast<int>((warps + 3) / 4);
+    attn_merge_kernel<<<blocks, 128, 0, st>>>(mp);
+    DKV_CUDA(cudaGetLastError());
+    return DKV_OK;
+}
+
+}  // namespace
+
+// ===========================================================================
+// Exported functions
+// ===========================================================================
+extern "C" {
+
+int dkv_version(void) { return 100; }
+
+const char* dkv_last_error(void) { return g_last_error.c_str(); }
+
+int dkv_context_create(int device, dkv_context** out) {
+    DKV_REQUIRE(out != nullptr, "out must not be NULL");
+    int ndev = 0;
+    DKV_CUDA(cudaGetDeviceCount(&ndev));
+    DKV_REQUIRE(device >= 0 && device < ndev, "device %d out of range (%d devices)", device, ndev);
+    DKV_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    DKV_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(DKV_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                    prop.major, prop.minor);
+    dkv_context* ctx = new dkv_context();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    cudaError_t e = cudaMalloc(&ctx->status, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->status, 0, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->counters, kMaxCounters * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->counters, 0, kMaxCounters * sizeof(unsigned int));
+    if (e == cudaSuccess) e = attn_set_attr<1, 8, 3>();
+    if (e == cudaSuccess) e = attn_set_attr<2, 8, 3>();
+    if (e == cudaSuccess) e = attn_set_attr<4, 8, 3>();
+    if (e == cudaSuccess) e = attn_set_attr<1, 12, 2>();
+    if (e == cudaSuccess) e = attn_set_attr<2, 12, 2>();
+    if (e == cudaSuccess) e = attn_set_attr<4, 12, 2>();
+    if (e == cudaSuccess) e = attn_set_attr<1, 16, 1>();
+    if (e == cudaSuccess) e = attn_set_attr<2, 16, 1>();
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(proj_rope_kernel<kProjStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kProjSmem));
+    if (e != cudaSuccess) {
+        delete ctx;
+        return fail(DKV_ERR_CUDA, "context set-up failed: %s", cudaGetErrorString(e));
+    }
+    *out = ctx;
+    return DKV_OK;
+}
+
+int dkv_context_destroy(dkv_context* ctx) {
+    if (!ctx) return DKV_OK;
+    cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->status) cudaFree(ctx->status);
+    if (ctx->counters) cudaFree(ctx->counters);
+    delete ctx;
+    return DKV_OK;
+}
+
+int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv, int hidden) {
+    DKV_REQUIRE(ctx != nullptr, "ctx is NULL");
+    DKV_REQUIRE(max_rows > 0 && nh_q > 0 && nh_kv > 0 && nh_q % nh_kv == 0, "bad reserve sizes");
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    ScratchPlan s = plan_scratch(ctx, max_rows, nh_q, nh_kv, hidden, hidden > 0, true);
+    return ensure_scratch(ctx, s.total);
+}
+
+int dkv_context_set(dkv_context* ctx, const char* key, int value) {
+    DKV_REQUIRE(ctx != nullptr && key != nullptr, "ctx / key is NULL");
+    if (!strcmp(key, "attn_variant")) {
+        DKV_REQUIRE(value >= 0 && value <= 2, "attn_variant must be 0..2");
+        ctx->attn_variant = value;
+    } else if (!strcmp(key, "attn_ctas")) {
+        DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
+        ctx->attn_ctas = value;
+    } else if (!strcmp(key, "proj_split_k")) {
+        DKV_REQUIRE(value >= 0 && value <= 256, "proj_split_k out of range");
+        ctx->proj_split_k = value;
+    } else {
+        return fail(DKV_ERR_INVALID, "unknown tuning key '%s'", key);
+    }
+    return DKV_OK;
+}
+
+int dkv_read_status(dkv_context* ctx, unsigned int* status, int clear) {
+    DKV_REQUIRE(ctx != nullptr && status != nullptr, "ctx / status is NULL");
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    DKV_CUDA(cudaDeviceSynchronize());
+    DKV_CUDA(cudaMemcpy(status, ctx->status, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+    if (clear && *status != 0) {
+        DKV_CUDA(cudaMemset(ctx->status, 0, sizeof(unsigned int)));
+        DKV_CUDA(cudaMemset(ctx->counters, 0, kMaxCounters * sizeof(unsigned int)));
+    }
+    return DKV_OK;
+}
+
+int dkv_layer_register(dkv_context* ctx, int layer_id, const dkv_layer_desc* desc) {
+    DKV_REQUIRE(ctx != nullptr && desc != nullptr, "ctx / desc is NULL");
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    LayerState L;
+    int rc = build_layer(&L, desc);
+    if (rc != DKV_OK) return rc;
+    ctx->layers[layer_id] = L;
+    return DKV_OK;
+}
+
+int dkv_layer_unregister(dkv_context* ctx, int layer_id) {
+    DKV_REQUIRE(ctx != nullptr, "ctx is NULL");
+    ctx->layers.erase(layer_id);
+    return DKV_OK;
+}
+
+int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) {
+    DKV_REQUIRE(ctx != nullptr && a != nullptr, "ctx / args is NULL");
+    auto it = ctx->layers.find(a->layer_id);
+    if (it == ctx->layers.end())
+        return fail(DKV_ERR_NOT_REGISTERED, "dkv_decode: layer %d not registered - call dkv_layer_register first",
+                    a->layer_id);
+    const LayerState& L = it->second;
+    const int nh_kv = L.d.nh_kv;
+    if (a->batch == 0) return DKV_OK;
+    DKV_REQUIRE(a->batch > 0, "batch must be >= 0");
+    DKV_REQUIRE(a->nh_q > 0 && a->nh_q % nh_kv == 0, "nh_q (%d) must be a multiple of nh_kv (%d)", a->nh_q, nh_kv);
+    DKV_REQUIRE(a->q != nullptr && a->seq_lens != nullptr, "q / seq_lens must not be NULL");
+    DKV_REQUIRE(a->out != nullptr || a->partial_out != nullptr, "out or partial_out must be given");
+    DKV_REQUIRE(a->q_stride >= static_cast<int64_t>(a->nh_q) * 128 && a->q_stride % 8 == 0, "q_stride too small or unaligned");
+    DKV_REQUIRE((reinterpret_cast<uintptr_t>(a->q) & 15) == 0, "q must be 16-byte aligned");
+    if (a->out) {
+        DKV_REQUIRE(a->out_stride >= static_cast<int64_t>(a->nh_q) * 128 && a->out_stride % 4 == 0, "out_stride too small or unaligned");
+        DKV_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & 7) == 0, "out must be 8-byte aligned");
+    }
+    const bool paged = a->page_table != nullptr;
+    if (paged) DKV_REQUIRE(a->pt_stride > 0, "pt_stride must be positive");
+    else DKV_REQUIRE(L.d.row_stride > 0, "layer was registered without row_stride; pass a page_table");
+    DKV_REQUIRE(a->new_mode >= DKV_NEW_NONE && a->new_mode <= DKV_NEW_GIVEN, "bad new_mode %d", a->new_mode);
+    if (a->new_mode == DKV_NEW_PROJECT) {
+        DKV_REQUIRE(L.has_weights, "layer %d has no projection weights registered", a->layer_id);
+        DKV_REQUIRE(a->x != nullptr && (reinterpret_cast<uintptr_t>(a->x) & 15) == 0, "x must be a 16-byte aligned device pointer");
+    }
+    if (a->new_mode == DKV_NEW_GIVEN) DKV_REQUIRE(a->k_new && a->v_new, "k_new / v_new must not be NULL");
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    const bool with_proj = a->new_mode == DKV_NEW_PROJECT;
+    ScratchPlan sp = plan_scratch(ctx, a->batch, a->nh_q, nh_kv, L.d.hidden, with_proj, false);
+    int rc = ensure_scratch(ctx, sp.total);
+    if (rc != DKV_OK) return rc;
+    uint8_t* base = ctx->scratch;
+    int* cum = reinterpret_cast<int*>(base + sp.cum);
+    int* tok_pos = reinterpret_cast<int*>(base + sp.tok_pos);
+    int* tok_slot = reinterpret_cast<int*>(base + sp.tok_slot);
+    __nv_bfloat16* kv_new = reinterpret_cast<__nv_bfloat16*>(base + sp.kv_new);
+    const int n_new = a->new_mode == DKV_NEW_NONE ? 0 : 1;
+
+    attn_prep_kernel<<<1, 256, 0, st>>>(a->seq_lens, a->batch, n_new, cum);
+    DKV_CUDA(cudaGetLastError());
+    if (n_new) {
+        decode_newtok_kernel<<<(a->batch + 127) / 128, 128, 0, st>>>(a->seq_lens, a->page_table, a->pt_stride, a->row_map,
+                                                                     a->batch, L.d.page_size, L.page_shift,
+                                                                     L.d.row_stride, a->save_kv_cache, tok_pos, tok_slot);
+        DKV_CUDA(cudaGetLastError());
+    }
+    if (a->new_mode == DKV_NEW_PROJECT) {
+        rc = launch_projection(ctx, L, a->x, a->batch, tok_pos, tok_slot, a->save_kv_cache != 0, kv_new,
+                               reinterpret_cast<float*>(base + sp.splitk), st);
+        if (rc != DKV_OK) return rc;
+    } else if (a->new_mode == DKV_NEW_GIVEN) {
+        const long long warps = static_cast<long long>(a->batch) * nh_kv;
+        store_new_kv_kernel<<<static_cast<int>((warps + 3) / 4), 128, 0, st>>>(
+            static_cast<const __nv_bfloat16*>(a->k_new), static_cast<const __nv_bfloat16*>(a->v_new), a->batch, nh_kv,
+            tok_slot, static_cast<__nv_bfloat16*>(L.k_dev), static_cast<__nv_bfloat16*>(L.v_dev), L.d.n_slots, kv_new,
+            ctx->status);
+        DKV_CUDA(cudaGetLastError());
+    }
+
+    AttnParams ap{};
+    ap.q = static_cast<const __nv_bfloat16*>(a->q);
+    ap.q_stride = a->q_stride;
+    ap.page_table = a->page_table;
+    ap.row_map = a->row_map;
+    ap.seq_lens = a->seq_lens;
+    ap.cum_tiles = cum;
+    ap.partials = reinterpret_cast<float*>(base + sp.partials);
+    ap.status = ctx->status;
+    ap.batch = a->batch;
+    ap.nh_q = a->nh_q;
+    ap.nh_kv = nh_kv;
+    ap.g_total = a->nh_q / nh_kv;
+    ap.pt_stride = a->pt_stride;
+    ap.page_size = L.d.page_size;
+    ap.page_shift = L.page_shift;
+    ap.rows_per_box = L.rows_per_box;
+    ap.row_stride = L.d.row_stride;
+    ap.n_new = n_new;
+    ap.scale_log2 = a->softmax_scale * 1.4426950408889634f;
+    MergeParams mp{};
+    mp.kv_new = n_new ? kv_new : nullptr;
+    mp.out = static_cast<__nv_bfloat16*>(a->out);
+    mp.out_stride = a->out_stride;
+    mp.lse = a->lse_out;
+    mp.part_out = a->partial_out;
+    return launch_attention(ctx, L, ap, paged, mp, st);
+}
+
+int dkv_merge_partials(dkv_context* ctx, const float* parts, int nranks, int64_t rows, void* out, float* lse,
+                       void* stream) {
+    DKV_REQUIRE(ctx != nullptr && parts != nullptr && out != nullptr, "NULL argument");
+    DKV_REQUIRE(nranks > 0 && rows > 0, "nranks and rows must be positive");
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    merge_rank_partials_kernel<<<static_cast<int>((rows + 3) / 4), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        parts, nranks, rows, static_cast<__nv_bfloat16*>(out), lse);
+    DKV_CUDA(cudaGetLastError());
+    return DKV_OK;
+}
+
+// Shared by the eager and the graph-safe extend entry points.
+static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, const void* Q, void* O, int B, int S_new,
+                      int nh_q, float scale, int is_causal, int seqlen_past, const int32_t* n_past_blocks_dev,
+                      int q_pos_start, const int32_t* row_map, cudaStream_t st) {
+    const int nh_kv = L.d.nh_kv;
+    const int64_t rows = static_cast<int64_t>(B) * S_new;
+    const bool qrot = (L.d.cos_sin != nullptr && q_pos_start >= 0);
+    ScratchPlan sp = plan_scratch(ctx, rows, nh_q, nh_kv, L.d.hidden, true, qrot);
+    int rc = ensure_scratch(ctx, sp.total);
+    if (rc != DKV_OK) return rc;
+    uint8_t* base = ctx->scratch;
+    int* cum = reinterpret_cast<int*>(base + sp.cum);
+    int* tok_pos = reinterpret_cast<int*>(base + sp.tok_pos);
+    int* tok_slot = reinterpret_cast<int*>(base + sp.tok_slot);
+    int* vseq = reinterpret_cast<int*>(base + sp.vseq);
+    int* vrow = reinterpret_cast<int*>(base + sp.vrow);
+
+    extend_prep_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, st>>>(
+        B, S_new, seqlen_past, n_past_blocks_dev, is_causal, row_map, L.d.row_stride, vseq, vrow, tok_pos, tok_slot);
+    DKV_CUDA(cudaGetLastError());
+    attn_prep_kernel<<<1, 256, 0, st>>>(vseq, static_cast<int>(rows), 0, cum);
+    DKV_CUDA(cudaGetLastError());
+    rc = launch_projection(ctx, L, X, static_cast<int>(rows), tok_pos, tok_slot, true, nullptr,
+                           reinterpret_cast<float*>(base + sp.splitk), st);
+    if (rc != DKV_OK) return rc;
+    const __nv_bfloat16* q_use = static_cast<const __nv_bfloat16*>(Q);
+    if (qrot) {
+        __nv_bfloat16* q_rot = reinterpret_cast<__nv_bfloat16*>(base + sp.q_rot);
+        const long long total = rows * nh_q * 64;
+        rope_q_kernel<<<static_cast<int>((total + 255) / 256), 256, 0, st>>>(q_use, q_rot, B, S_new, nh_q, L.d.cos_sin,
+                                                                           L.d.max_pos, q_pos_start, ctx->status);
+        DKV_CUDA(cudaGetLastError());
+        q_use = q_rot;
+    }
+    AttnParams ap{};
+    ap.q = q_use;
+    ap.q_stride = static_cast<long long>(nh_q) * 128;
+    ap.page_table = nullptr;
+    ap.row_map = vrow;
+    ap.seq_lens = vseq;
+    ap.cum_tiles = cum;
+    ap.partials = reinterpret_cast<float*>(base + sp.partials);
+    ap.status = ctx->status;
+    ap.batch = static_cast<int>(rows);
+    ap.nh_q = nh_q;
+    ap.nh_kv = nh_kv;
+    ap.g_total = nh_q / nh_kv;
+    ap.page_size = 1;
+    ap.page_shift = 0;
+    ap.rows_per_box = kTileTokens;
+    ap.row_stride = L.d.row_stride;
+    ap.n_new = 0;
+    ap.scale_log2 = scale * 1.4426950408889634f;
+    MergeParams mp{};
+    mp.out = static_cast<__nv_bfloat16*>(O);
+    mp.out_stride = static_cast<long long>(nh_q) * 128;
+    return launch_attention(ctx, L, ap, false, mp, st);
+}
+
+int dkv_smpv2_fwd(dkv_context* ctx, const void* X, const void* Wk, const void* Wv, const void* Q, void* K_cpu,
+                  void* V_cpu, const float* cos_sin, int max_pos, int B, int S_new, int H, int nh_q, int nh_kv,
+                  int S_total, float softmax_scale, int is_causal, int seqlen_past, int q_pos_start, void* O,
+                  void* stream) {
+    DKV_REQUIRE(ctx != nullptr, "ctx is NULL");
+    DKV_REQUIRE(X && Wk && Wv && Q && K_cpu && V_cpu && O, "NULL tensor pointer");
+    DKV_REQUIRE(B > 0 && S_new > 0 && H > 0 && nh_q > 0 && nh_kv > 0, "sizes must be positive");
+    // directkv/kernel/smpv2_extension.cu:176-178
+    DKV_REQUIRE(S_total == seqlen_past + S_new, "K_cpu S_total (%d) != seqlen_past (%d) + S_new (%d)", S_total, seqlen_past, S_new);
+    // directkv/kernel/smpv2_extension.cu:606-609
+    DKV_REQUIRE(nh_q % nh_kv == 0, "Q.size(2) (NH_q=%d) must be a multiple of Wk.size(0) (NH_kv=%d)", nh_q, nh_kv);
+    DKV_REQUIRE(seqlen_past >= 0, "seqlen_past must be >= 0");
+    DKV_REQUIRE(H % 64 == 0, "hidden size (%d) must be a multiple of 64", H);
+    DKV_REQUIRE((reinterpret_cast<uintptr_t>(X) & 15) == 0 && (reinterpret_cast<uintptr_t>(Q) & 15) == 0 &&
+                    (reinterpret_cast<uintptr_t>(Wk) & 15) == 0 && (reinterpret_cast<uintptr_t>(Wv) & 15) == 0,
+                "X, Q, Wk, Wv must be 16-byte aligned");
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    dkv_layer_desc d{};
+    d.k_pool = K_cpu;
+    d.v_pool = V_cpu;
+    d.n_slots = static_cast<int64_t>(B) * S_total;
+    d.nh_kv = nh_kv;
+    d.page_size = 1;
+    d.row_stride = S_total;
+    d.wk = Wk;
+    d.wv = Wv;
+    d.hidden = H;
+    d.cos_sin = cos_sin;
+    d.max_pos = max_pos;
+    LayerState L;
+    int rc = build_layer(&L, &d);
+    if (rc != DKV_OK) return rc;
+    return run_extend(ctx, L, X, Q, O, B, S_new, nh_q, softmax_scale, is_causal, seqlen_past, nullptr, q_pos_start,
+                      nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int dkv_smpv2_fwd_graph(dkv_context* ctx, int layer_id, const void* X_pad, const void* Q_pad, void* O_out,
+                        const int32_t* n_past_blocks_dev, int B, int S_new, int nh_q, float softmax_scale,
+                        int is_causal, const int32_t* req_pool_indices, void* stream) {
+    DKV_REQUIRE(ctx != nullptr, "ctx is NULL");
+    auto it = ctx->layers.find(layer_id);
+    if (it == ctx->layers.end())
+        return fail(DKV_ERR_NOT_REGISTERED, "smpv2_fwd_graph: layer %d not initialized - call smpv2_init_tma first", layer_id);
+    const LayerState& L = it->second;
+    DKV_REQUIRE(X_pad && Q_pad && O_out && n_past_blocks_dev, "NULL tensor pointer");
+    DKV_REQUIRE(B > 0 && S_new > 0 && nh_q > 0 && nh_q % L.d.nh_kv == 0, "bad sizes");
+    DKV_REQUIRE(L.has_weights, "layer %d has no projection weights registered", layer_id);
+    DKV_REQUIRE(L.d.row_stride > 0, "layer %d was registered without row_stride", layer_id);
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    return run_extend(ctx, L, X_pad, Q_pad, O_out, B, S_new, nh_q, softmax_scale, is_causal, 0, n_past_blocks_dev, -1,
+                      req_pool_indices, static_cast<cudaStream_t>(stream));
+}
+
+int dkv_extend(dkv_context* ctx, int layer_id, const void* X, const void* Q, void* O, int B, int S_new, int nh_q,
+               float softmax_scale, int is_causal, int seqlen_past, int q_pos_start, const int32_t* row_map,
+               void* stream) {
+    DKV_REQUIRE(ctx != nullptr, "ctx is NULL");
+    auto it = ctx->layers.find(layer_id);
+    if (it == ctx->layers.end())
+        return fail(DKV_ERR_NOT_REGISTERED, "dkv_extend: layer %d not registered - call dkv_layer_register first", layer_id);
+    const LayerState& L = it->second;
+    DKV_REQUIRE(X && Q && O, "NULL tensor pointer");
+    DKV_REQUIRE(B > 0 && S_new > 0 && nh_q > 0 && nh_q % L.d.nh_kv == 0, "bad sizes");
+    DKV_REQUIRE(seqlen_past >= 0, "seqlen_past must be >= 0");
+    DKV_REQUIRE(L.has_weights, "layer %d has no projection weights registered", layer_id);
+    DKV_REQUIRE(L.d.row_stride > 0, "layer %d was registered without row_stride", layer_id);
+    DKV_REQUIRE(seqlen_past + S_new <= L.d.row_stride, "seqlen_past + S_new (%d) exceeds the pool row (%lld)",
+                seqlen_past + S_new, (long long)L.d.row_stride);
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    return run_extend(ctx, L, X, Q, O, B, S_new, nh_q, softmax_scale, is_causal, seqlen_past, nullptr, q_pos_start,
+                      row_map, static_cast<cudaStream_t>(stream));
+}
+
+int dkv_scatter_kv(dkv_context* ctx, void* k_pool, void* v_pool, int64_t n_slots, int64_t k_row_bytes,
+                   int64_t v_row_bytes, const void* loc, int loc_is_int64, const void* cache_k, const void* cache_v,
+                   int64_t n_tokens, void* stream) {
+    DKV_REQUIRE(ctx != nullptr && k_pool && v_pool && loc && cache_k && cache_v, "NULL argument");
+    DKV_REQUIRE(n_slots > 0 && n_tokens >= 0, "bad sizes");
+    DKV_REQUIRE(k_row_bytes > 0 && k_row_bytes % 16 == 0 && v_row_bytes > 0 && v_row_bytes % 16 == 0,
+                "token rows must be multiples of 16 bytes");
+    if (n_tokens == 0) return DKV_OK;
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    void *kd = nullptr, *vd = nullptr;
+    int rc = device_pointer_of(k_pool, &kd, "k_pool");
+    if (rc != DKV_OK) return rc;
+    if ((rc = device_pointer_of(v_pool, &vd, "v_pool")) != DKV_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = static_cast<int>(n_tokens);
+    if (loc_is_int64) {
+        scatter_rows_kernel<long long><<<grid, 128, 0, st>>>(static_cast<uint4*>(kd), static_cast<const uint4*>(cache_k),
+                                                            static_cast<const long long*>(loc), n_slots,
+                                                            static_cast<int>(k_row_bytes / 16), ctx->status);
+        scatter_rows_kernel<long long><<<grid, 128, 0, st>>>(static_cast<uint4*>(vd), static_cast<const uint4*>(cache_v),
+                                                            static_cast<const long long*>(loc), n_slots,
+                                                            static_cast<int>(v_row_bytes / 16), ctx->status);
+    } else {
+        scatter_rows_kernel<int><<<grid, 128, 0, st>>>(static_cast<uint4*>(kd), static_cast<const uint4*>(cache_k),
+                                                      static_cast<const int*>(loc), n_slots,
+                                                      static_cast<int>(k_row_bytes / 16), ctx->status);
+        scatter_rows_kernel<int><<<grid, 128, 0, st>>>(static_cast<uint4*>(vd), static_cast<const uint4*>(cache_v),
+                                                      static_cast<const int*>(loc), n_slots,
+                                                      static_cast<int>(v_row_bytes / 16), ctx->status);
+    }
+    DKV_CUDA(cudaGetLastError());
+    return DKV_OK;
+}
+
+int dkv_stream_copy(dkv_context* ctx, void* dst, const void* src, int64_t bytes, void* stream) {
+    DKV_REQUIRE(ctx != nullptr && dst != nullptr && src != nullptr, "NULL argument");
+    DKV_REQUIRE(bytes > 0 && bytes % 16 == 0, "bytes must be a positive multiple of 16");
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    void* src_dev = nullptr;
+    int rc = device_pointer_of(const_cast<void*>(src), &src_dev, "src");
+    if (rc != DKV_OK) return rc;
+    stream_copy_kernel<<<ctx->sm_count * 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint4*>(dst), static_cast<const uint4*>(src_dev), bytes / 16);
+    DKV_CUDA(cudaGetLastError());
+    return DKV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,195 @@
+/*
+ * directkv_b200 - C ABI of the B200 (sm_100a) decode-attention engine.
+ *
+ * This is the drop-in boundary for the reference's extension module
+ * (directkv/kernel/smpv2_extension.cu, loaded by directkv/kernel/__init__.py): plain pointers,
+ * sizes and a stream handle go in, an int status comes out.  No torch types appear here; the
+ * Python package turns tensors into pointers and a non-zero status into RuntimeError, which
+ * is what the reference's TORCH_CHECK failures surface as.
+ *
+ * Conventions
+ *  - bf16 everywhere for Q/K/V/X/W/O; head_dim is 128 (directkv/directkv_backend.py:163-169).
+ *  - KV pools are [n_slots, nh_kv, 128] bf16, in host-pinned (mapped) memory or in device
+ *    memory: the layout of DirectKVTokenToKVPool (directkv/directkv_pool.py:96-130) and, with
+ *    slot = row * row_stride + position, of DirectKVRequestPool
+ *    (directkv/directkv_request_pool.py:66-76).
+ *  - `stream` is a cudaStream_t passed as void*; every call only enqueues work unless said
+ *    otherwise.  Pointers must stay valid until that work has run.
+ *  - All functions return DKV_OK or an error code; dkv_last_error() gives the text for the
+ *    calling thread.
+ *  - A context belongs to one device and one host thread at a time (the reference's module is
+ *    likewise single-threaded per process: directkv/kernel/smpv2_extension.cu:53-61).
+ */
+#ifndef DIRECTKV_B200_H
+#define DIRECTKV_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DKV_OK                  0
+#define DKV_ERR_INVALID         1   /* bad argument (reference: TORCH_CHECK -> RuntimeError) */
+#define DKV_ERR_CUDA            2   /* a CUDA runtime/driver call failed */
+#define DKV_ERR_UNSUPPORTED     3   /* shape outside what the kernels handle */
+#define DKV_ERR_NOT_REGISTERED  4   /* layer id unknown (reference: "call smpv2_init_tma first") */
+#define DKV_ERR_DEVICE_STATUS   5   /* the device status word is non-zero (bounded wait ran out, bad slot) */
+
+/* Bits of the device status word (dkv_read_status). */
+#define DKV_STATUS_WAIT_TIMEOUT  (1u << 0)
+#define DKV_STATUS_BAD_SLOT      (1u << 1)
+#define DKV_STATUS_BAD_POSITION  (1u << 2)
+#define DKV_STATUS_TMEM_TIMEOUT  (1u << 3)
+
+/* How the token decoded in this step enters dkv_decode. */
+#define DKV_NEW_NONE     0   /* every attended token is already in the pool */
+#define DKV_NEW_PROJECT  1   /* K/V = X . Wk^T / Wv^T on tensor cores, Neox RoPE on K, stored to the pool */
+#define DKV_NEW_GIVEN    2   /* caller passes the token's (already rotated) K/V rows */
+
+typedef struct dkv_context dkv_context;
+
+int         dkv_version(void);
+const char* dkv_last_error(void);
+
+/* One context per device: owns scratch memory, the status word and the per-layer tables. */
+int dkv_context_create(int device, dkv_context** out);
+int dkv_context_destroy(dkv_context* ctx);
+
+/*
+ * Pre-sizes scratch so that later calls with batch <= max_rows query rows
+ * (requests for decode, batch * S_new for dkv_smpv2_fwd), nh_q/nh_kv heads and hidden size
+ * allocate nothing (needed before CUDA-graph capture; the reference pre-allocates in
+ * smpv2_init_tma, directkv/kernel/smpv2_extension.cu:412-422).
+ */
+int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv, int hidden);
+
+/* Tuning knobs, by name: "attn_variant" (0..2), "attn_ctas" (CTAs of the streaming kernel,
+ * 0 = one per SM), "proj_split_k" (0 = automatic). */
+int dkv_context_set(dkv_context* ctx, const char* key, int value);
+
+/* Blocks until the stream work touching the status word is done is NOT implied: this
+ * synchronises the device, copies the status word and optionally clears it. */
+int dkv_read_status(dkv_context* ctx, unsigned int* status, int clear);
+
+/*
+ * Per-layer registration: replaces smpv2_init_tma(layer_id, X_max, Wk, Wv, Q_max, K_max, V_max)
+ * (directkv/kernel/smpv2_extension.cu:363-423).  Builds and caches the TMA descriptors of the
+ * KV pool and of the projection weights.  Pointers must stay valid while the layer is
+ * registered.  wk/wv/cos_sin may be NULL for an attention-only layer.
+ */
+typedef struct {
+    void*        k_pool;      /* [n_slots, nh_kv, 128] bf16; host-pinned or device */
+    void*        v_pool;
+    int64_t      n_slots;
+    int          nh_kv;
+    int          page_size;   /* tokens per page, power of two >= 1 (paged calls) */
+    int64_t      row_stride;  /* slots per pool row (calls with page_table == NULL) */
+    const void*  wk;          /* [nh_kv, 128, hidden] bf16, device */
+    const void*  wv;
+    int          hidden;      /* multiple of 64 */
+    const float* cos_sin;     /* [max_pos, 128] fp32 = [cos | sin], device; NULL = no RoPE (OPT) */
+    int          max_pos;
+} dkv_layer_desc;
+
+int dkv_layer_register(dkv_context* ctx, int layer_id, const dkv_layer_desc* desc);
+int dkv_layer_unregister(dkv_context* ctx, int layer_id);
+
+/*
+ * One decode step of one layer for a ragged batch: replaces the kernel path of
+ * DirectKVBackend.forward_decode (directkv/directkv_backend.py:527-627) and, for every length,
+ * its torch path _sdpa_decode_directkv (:781-825) / _sdpa_decode_manual (:835-859).
+ *
+ * Token t of request b lives at slot
+ *     page_table[row(b), t / page_size] * page_size + t % page_size        (paged)
+ *     row(b) * row_stride + t                                              (page_table == NULL)
+ * with row(b) = row_map ? row_map[b] : b.  seq_lens[b] counts the tokens attended, including
+ * the token decoded now unless new_mode == DKV_NEW_NONE.  All index arrays are int32 in
+ * device memory and are read on the device, so the call can be captured in a CUDA graph and
+ * replayed with new lengths.
+ */
+typedef struct {
+    int            layer_id;
+    int            batch;
+    int            nh_q;
+    const void*    q;            /* bf16 device, row b at q + b * q_stride elements, [nh_q, 128] */
+    int64_t        q_stride;
+    void*          out;          /* bf16 device, row b at out + b * out_stride; may be NULL */
+    int64_t        out_stride;
+    const int32_t* seq_lens;     /* [batch] */
+    const int32_t* page_table;   /* [rows, pt_stride] or NULL */
+    int            pt_stride;
+    const int32_t* row_map;      /* [batch] or NULL */
+    int            new_mode;     /* DKV_NEW_* */
+    const void*    x;            /* [batch, hidden] bf16 device (DKV_NEW_PROJECT) */
+    const void*    k_new;        /* [batch, nh_kv, 128] bf16 device (DKV_NEW_GIVEN) */
+    const void*    v_new;
+    int            save_kv_cache;/* store the new token's K/V to the pool */
+    float          softmax_scale;
+    float*         lse_out;      /* [batch, nh_q] natural-log LSE, or NULL */
+    float*         partial_out;  /* [batch, nh_q, 132] unnormalised (O[128], m_log2, l, pad) or NULL */
+} dkv_decode_args;
+
+int dkv_decode(dkv_context* ctx, const dkv_decode_args* args, void* stream);
+
+/* Combines nranks sets of unnormalised partials [nranks, rows, 132] (sequence split across
+ * GPUs, after the all-gather) into bf16 out [rows, 128] and optional lse [rows]. */
+int dkv_merge_partials(dkv_context* ctx, const float* parts, int nranks, int64_t rows, void* out, float* lse,
+                       void* stream);
+
+/*
+ * Same argument meaning as the reference's smpv2_fwd(X, Wk, Wv, Q, K_cpu, V_cpu, cos_sin,
+ * softmax_scale, is_causal, seqlen_past, q_pos_start) -> O
+ * (directkv/kernel/smpv2_extension.cu:574-637): projects the S_new new rows, rotates K at
+ * positions seqlen_past.., stores them into K_cpu/V_cpu[:, seqlen_past:], and attends every new
+ * row over past + new rows (causal offset seqlen_past).  Differences: the projection runs over
+ * the full hidden size, and seqlen_past / S_new need not be multiples of 64.
+ * X [B,S_new,H], Q/O [B,S_new,nh_q,128] device; K_cpu/V_cpu [B,S_total,nh_kv,128] pinned host
+ * or device, S_total == seqlen_past + S_new.
+ */
+int dkv_smpv2_fwd(dkv_context* ctx, const void* X, const void* Wk, const void* Wv, const void* Q, void* K_cpu,
+                  void* V_cpu, const float* cos_sin, int max_pos, int B, int S_new, int H, int nh_q, int nh_kv,
+                  int S_total, float softmax_scale, int is_causal, int seqlen_past, int q_pos_start, void* O,
+                  void* stream);
+
+/*
+ * Graph-safe form, replacing smpv2_fwd_graph (directkv/kernel/smpv2_extension.cu:436-569): the
+ * layer must be registered; the number of past 64-token blocks is read from device memory
+ * (n_past_blocks_dev, int32) when the work runs; req_pool_indices ([B] int32 device or NULL)
+ * maps batch position to pool row (csrc/directKV_kernel.cuh:224-226).  Allocates nothing after
+ * dkv_context_reserve.
+ */
+int dkv_smpv2_fwd_graph(dkv_context* ctx, int layer_id, const void* X_pad, const void* Q_pad, void* O_out,
+                        const int32_t* n_past_blocks_dev, int B, int S_new, int nh_q, float softmax_scale,
+                        int is_causal, const int32_t* req_pool_indices, void* stream);
+
+/*
+ * Extend / chunked prefill of registered pool rows: the kernel call of
+ * DirectKVBackend.forward_extend (directkv/directkv_backend.py:681-697) without rebuilding
+ * descriptors.  Request b uses pool row row_map[b] (or b); its S_new new rows are projected,
+ * rotated at positions seqlen_past.., stored at [row, seqlen_past + i] and attend past + new
+ * rows.  X [B,S_new,H], Q/O [B,S_new,nh_q,128] bf16 device.
+ */
+int dkv_extend(dkv_context* ctx, int layer_id, const void* X, const void* Q, void* O, int B, int S_new, int nh_q,
+               float softmax_scale, int is_causal, int seqlen_past, int q_pos_start, const int32_t* row_map,
+               void* stream);
+
+/*
+ * Stream-ordered store of new tokens into a token-indexed pool: replaces the blocking
+ * device-to-host copy plus CPU scatter of DirectKVTokenToKVPool.set_kv_buffer
+ * (directkv/directkv_pool.py:174-209).  Row i of cache_k / cache_v ([n_tokens, row_bytes],
+ * device) is written to slot loc[i] of the pool ([n_slots, row_bytes], host-pinned or device)
+ * by a kernel, with no host synchronisation.  loc is int32 or int64 in device memory.
+ */
+int dkv_scatter_kv(dkv_context* ctx, void* k_pool, void* v_pool, int64_t n_slots, int64_t k_row_bytes,
+                   int64_t v_row_bytes, const void* loc, int loc_is_int64, const void* cache_k, const void* cache_v,
+                   int64_t n_tokens, void* stream);
+
+/* Host-link helper: device-side copy kernel reading `bytes` from src (host-mapped or device)
+ * into dst (device) with plain vector loads; used to measure the zero-copy roofline. */
+int dkv_stream_copy(dkv_context* ctx, void* dst, const void* src, int64_t bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DIRECTKV_B200_H */

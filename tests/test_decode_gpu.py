@@ -1,0 +1,185 @@
+"""GPU parity of the decode path (dkv_decode through the C ABI) against the CPU oracle."""
+
+import math
+
+import pytest
+import torch
+
+from dkv_testlib import KV_ATOL, assert_close, orc
+
+pytestmark = pytest.mark.gpu
+
+from directkv_b200 import kernel, workloads  # noqa: E402
+from directkv_b200._lib import PARTIAL_STRIDE, get_context  # noqa: E402
+
+DEV = "cuda:0"
+
+
+def _shape(hidden, nh_q, nh_kv, rope=True):
+    return workloads.LayerShape(f"t{hidden}-{nh_q}-{nh_kv}", hidden, nh_q, nh_kv, 10000.0 if rope else None)
+
+
+def _run_decode(shape, seq_lens, page_size, cfg_id, kv_on_host=True, mode="project", variant=0, lid=7):
+    case = workloads.make_decode_case(shape, seq_lens, page_size, cfg_id, DEV, kv_on_host=kv_on_host)
+    k_ref, v_ref = case["k_pool"].cpu().clone(), case["v_pool"].cpu().clone()
+    k_before = k_ref.clone()
+    ctx = get_context(0)
+    ctx.set("attn_variant", variant)
+    kernel.register_layer(lid, case["k_pool"], case["v_pool"], case["wk"], case["wv"], case["cos_sin"],
+                          page_size=page_size)
+    cs_cpu = None if case["cos_sin"] is None else case["cos_sin"].cpu()
+    kw = {}
+    if mode == "project":
+        kw["x"] = case["x"]
+        ref = orc.decode_layer(case["x"].cpu(), case["wk"].cpu(), case["wv"].cpu(), case["q"].cpu(), k_ref, v_ref,
+                               case["page_table"].cpu(), seq_lens, page_size, cs_cpu, shape.scale)
+    elif mode == "given":
+        kn, vn = orc.project_kv(case["x"].cpu(), case["wk"].cpu(), case["wv"].cpu())
+        kw["k_new"], kw["v_new"] = kn.to(DEV), vn.to(DEV)
+        ref = orc.decode_layer(None, None, None, case["q"].cpu(), k_ref, v_ref, case["page_table"].cpu(), seq_lens,
+                               page_size, None, shape.scale, k_new=kn, v_new=vn)
+    else:
+        ref = orc.decode_layer(None, None, None, case["q"].cpu(), k_ref, v_ref, case["page_table"].cpu(), seq_lens,
+                               page_size, None, shape.scale)
+    out = kernel.decode(lid, case["q"], case["seq_lens"], shape.scale, page_table=case["page_table"], **kw)
+    ctx.raise_on_status()
+    assert_close(out, ref.view_as(out), "O")
+    ctx.set("attn_variant", 0)
+    if mode != "none":
+        # Stored K/V of the new token: within the reference's write-back threshold; every other slot untouched.
+        k_now, v_now = case["k_pool"].cpu(), case["v_pool"].cpu()
+        touched = torch.zeros(k_now.shape[0], dtype=torch.bool)
+        for b, sl in enumerate(seq_lens):
+            slot = orc.token_slot(case["page_table"][b].tolist(), sl - 1, page_size)
+            touched[slot] = True
+            assert_close(k_now[slot], k_ref[slot], f"K write-back req {b}", atol=KV_ATOL, rtol=RTOL_KV)
+            assert_close(v_now[slot], v_ref[slot], f"V write-back req {b}", atol=KV_ATOL, rtol=RTOL_KV)
+        assert torch.equal(k_now[~touched], k_before[~touched]), "past K slots must be bit-identical"
+    kernel.unregister_layer(lid)
+    return out
+
+
+RTOL_KV = 1e-2
+
+
+@pytest.mark.parametrize("nh_q,nh_kv", [(4, 4), (8, 2), (6, 3), (7, 7), (8, 1), (12, 2)])
+def test_head_groupings(nh_q, nh_kv):
+    _run_decode(_shape(256, nh_q, nh_kv), [1, 2, 17, 40, 129, 300], 16, cfg_id=1)
+
+
+@pytest.mark.parametrize("page_size", [1, 2, 4, 8, 16, 32, 64])
+def test_page_sizes(page_size):
+    _run_decode(_shape(128, 4, 2), [1, 5, 16, 31, 64, 65, 200, 333], page_size, cfg_id=2)
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+def test_kernel_variants(variant):
+    _run_decode(_shape(128, 8, 4), [3, 100, 257, 1000, 48, 16], 16, cfg_id=3, variant=variant)
+
+
+@pytest.mark.parametrize("mode", ["project", "given", "none"])
+def test_new_token_modes(mode):
+    _run_decode(_shape(192, 4, 4, rope=(mode == "project")), [9, 77, 130, 16, 1 if mode != "none" else 2], 16,
+                cfg_id=4, mode=mode)
+
+
+def test_hbm_resident_pool():
+    _run_decode(_shape(256, 8, 8, rope=False), [700, 64, 1, 15, 2048], 16, cfg_id=5, kv_on_host=False)
+
+
+def test_config1_llama3_8b_layer():
+    """BASELINE config 1: Llama-3-8B layer, batch 1, 4096 cached tokens + the decoded one, RoPE theta 5e5."""
+    _run_decode(workloads.LLAMA3_8B, [4097], 16, cfg_id=0)
+
+
+def test_config2_shape_opt67b_ragged_small():
+    """Config 2 geometry (32 MHA heads, hidden 4096, 16-token permuted pages, 16 ragged requests) at short lengths."""
+    lens = workloads.ragged_lengths_uniform(16, 8, 300, seed=4235)
+    _run_decode(workloads.OPT_6_7B, lens, 16, cfg_id=1)
+
+
+def test_config5_shape_opt30b_shard():
+    """Config 5 geometry on one GPU of eight: 7 MHA heads, hidden 7168."""
+    _run_decode(workloads.OPT_30B.shard(8), [513, 1024, 37], 16, cfg_id=5)
+
+
+def test_contiguous_rows_and_row_map():
+    """Request-pool layout: slot = row * row_stride + position, with a row map."""
+    shape = _shape(128, 4, 2)
+    rows, s_pad = 5, 256
+    g = torch.Generator().manual_seed(11)
+    k_pool = (torch.randn(rows, s_pad, 2, 128, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    v_pool = (torch.randn(rows, s_pad, 2, 128, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    seq_lens = [200, 1, 64]
+    row_map = [4, 0, 2]
+    q = (torch.randn(3, 4, 128, generator=g)).to(torch.bfloat16)
+    kn = (torch.randn(3, 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+    vn = (torch.randn(3, 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+    k_ref, v_ref = k_pool.clone().view(-1, 2, 128), v_pool.clone().view(-1, 2, 128)
+    table = torch.tensor([[r * s_pad + t for t in range(s_pad)] for r in row_map], dtype=torch.int32)
+    ref = orc.decode_layer(None, None, None, q, k_ref, v_ref, table, seq_lens, 1, None, shape.scale, k_new=kn, v_new=vn)
+    kernel.register_layer(21, k_pool, v_pool, row_stride=s_pad)
+    out = kernel.decode(21, q.to(DEV), torch.tensor(seq_lens, dtype=torch.int32, device=DEV), shape.scale,
+                        row_map=torch.tensor(row_map, dtype=torch.int32, device=DEV), k_new=kn.to(DEV), v_new=vn.to(DEV))
+    get_context(0).raise_on_status()
+    assert_close(out, ref, "O")
+    for b, (r, sl) in enumerate(zip(row_map, seq_lens)):
+        assert torch.equal(k_pool[r, sl - 1], kn[b]) and torch.equal(v_pool[r, sl - 1], vn[b])
+    kernel.unregister_layer(21)
+
+
+def test_lse_and_sequence_split_merge():
+    """Sequence split emulated on one GPU: two token ranges of one request produce unnormalised
+    partials whose merge equals attention over the whole range (and the LSE matches)."""
+    shape = _shape(128, 8, 2, rope=False)
+    total = 1000
+    case = workloads.make_decode_case(shape, [total], 16, 9, DEV)
+    kernel.register_layer(31, case["k_pool"], case["v_pool"], page_size=16)
+    q = case["q"]
+    ref, lse_ref = orc.decode_layer(None, None, None, q.cpu(), case["k_pool"].cpu(), case["v_pool"].cpu(),
+                                    case["page_table"].cpu(), [total], 16, None, shape.scale, return_lse=True)
+    lse = torch.empty(1, 8, dtype=torch.float32, device=DEV)
+    out = kernel.decode(31, q, case["seq_lens"], shape.scale, page_table=case["page_table"], lse_out=lse)
+    assert_close(out, ref, "O")
+    assert_close(lse, lse_ref, "LSE", atol=2e-3, rtol=1e-3)
+    split = 512  # page aligned
+    parts = torch.zeros(2, 8, PARTIAL_STRIDE, dtype=torch.float32, device=DEV)
+    lens0 = torch.tensor([split], dtype=torch.int32, device=DEV)
+    lens1 = torch.tensor([total - split], dtype=torch.int32, device=DEV)
+    kernel.decode(31, q, lens0, shape.scale, page_table=case["page_table"], partial_out=parts[0], normalized=False)
+    kernel.decode(31, q, lens1, shape.scale, page_table=case["page_table"][:, split // 16:].contiguous(),
+                  partial_out=parts[1], normalized=False)
+    lse2 = torch.empty(8, dtype=torch.float32, device=DEV)
+    merged = kernel.merge_partials(parts, lse_out=lse2)
+    get_context(0).raise_on_status()
+    assert_close(merged.view(1, 8, 128), ref, "merged O")
+    assert_close(lse2.view(1, 8), lse_ref, "merged LSE", atol=2e-3, rtol=1e-3)
+    kernel.unregister_layer(31)
+
+
+def test_larger_ragged_batch_balance():
+    """64 requests with very uneven lengths (lognormal), GQA 4:1: exercises the even split of tiles over warps."""
+    lens = workloads.ragged_lengths_lognormal(64, 600, 1.0, 1, 6000, seed=4238)
+    _run_decode(_shape(128, 8, 2), lens, 16, cfg_id=6)
+
+
+def test_errors():
+    with pytest.raises(RuntimeError, match="not registered"):
+        kernel.decode(999, torch.zeros(1, 128, dtype=torch.bfloat16, device=DEV),
+                      torch.ones(1, dtype=torch.int32, device=DEV), 1.0)
+    pool = torch.zeros(32, 2, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="pinned"):
+        kernel.register_layer(1, pool, pool)
+    pk = torch.zeros(32, 2, 128, dtype=torch.bfloat16).pin_memory()
+    kernel.register_layer(41, pk, pk.clone().pin_memory(), page_size=16)
+    with pytest.raises(RuntimeError, match="multiple"):
+        kernel.decode(41, torch.zeros(1, 3 * 128, dtype=torch.bfloat16, device=DEV),
+                      torch.ones(1, dtype=torch.int32, device=DEV), 1.0,
+                      page_table=torch.ones(1, 1, dtype=torch.int32, device=DEV))
+    kernel.unregister_layer(41)
+
+
+def test_empty_batch():
+    q = torch.zeros(0, 4 * 128, dtype=torch.bfloat16, device=DEV)
+    out = kernel.decode(0, q, torch.zeros(0, dtype=torch.int32, device=DEV), 1.0)
+    assert out.shape == q.shape

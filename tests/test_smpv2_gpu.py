@@ -1,0 +1,149 @@
+"""GPU parity of the reference-shaped entry points (smpv2_fwd / smpv2_init_tma / smpv2_fwd_graph).
+
+The first block replays the 12 seeded cases of the reference's kernel test
+(tests/test_directkv_cpu_kv.cu:538-557) with its libc rand() input streams and its pass
+criteria (:478-483); the second covers what that test never exercises: hidden sizes above 128
+on the tensor-core projection, Neox RoPE, GQA, lengths that are not multiples of 64.
+"""
+
+import pytest
+import torch
+
+from dkv_testlib import KAT_CASES, KV_ATOL, assert_close, kat_inputs, orc
+
+pytestmark = pytest.mark.gpu
+
+from directkv_b200 import kernel  # noqa: E402
+from directkv_b200._lib import get_context  # noqa: E402
+
+DEV = "cuda:0"
+SCALE = 128 ** -0.5
+
+
+def _run_fwd(X, Wk, Wv, Q, K, V, cos_sin, causal, s_past, q_pos_start=-1, kv_on_host=True):
+    K_ref, V_ref = K.clone(), V.clone()
+    ref = orc.smpv2_fwd(X, Wk, Wv, Q, K_ref, V_ref, cos_sin, SCALE, causal, s_past, q_pos_start)
+    Kd = K.clone().pin_memory() if kv_on_host else K.to(DEV)
+    Vd = V.clone().pin_memory() if kv_on_host else V.to(DEV)
+    cs = None if cos_sin is None else cos_sin.to(DEV)
+    O = kernel.smpv2_fwd(X.to(DEV), Wk.to(DEV), Wv.to(DEV), Q.to(DEV), Kd, Vd, cs, SCALE, causal, s_past, q_pos_start)
+    get_context(0).raise_on_status()
+    o_err = assert_close(O, ref, "O")
+    # K/V write-back of the new rows (reference thresholds), past rows bit-identical.
+    assert_close(Kd.cpu()[:, s_past:], K_ref[:, s_past:], "K write-back", atol=KV_ATOL, rtol=1e-2)
+    assert_close(Vd.cpu()[:, s_past:], V_ref[:, s_past:], "V write-back", atol=KV_ATOL, rtol=1e-2)
+    if s_past > 0:
+        assert torch.equal(Kd.cpu()[:, :s_past], K[:, :s_past]) and torch.equal(Vd.cpu()[:, :s_past], V[:, :s_past])
+    return o_err
+
+
+@pytest.mark.parametrize("name,B,NH,S_new,S_past,H,causal", KAT_CASES, ids=[c[0] for c in KAT_CASES])
+def test_reference_kat_cases(oracle_clib, name, B, NH, S_new, S_past, H, causal):
+    X, Wk, Wv, Q, K, V = kat_inputs(oracle_clib, B, NH, S_new, S_past, H)
+    o_err = _run_fwd(X, Wk, Wv, Q, K, V, None, causal, S_past)
+    assert o_err < 2e-2  # tests/test_directkv_cpu_kv.cu:478
+
+
+def _rand_case(B, nh_q, nh_kv, S_new, S_past, H, seed, rope=True):
+    g = torch.Generator().manual_seed(seed)
+    X = torch.randn(B, S_new, H, generator=g).to(torch.bfloat16)
+    Wk = (torch.randn(nh_kv, 128, H, generator=g) * 0.02).to(torch.bfloat16)
+    Wv = (torch.randn(nh_kv, 128, H, generator=g) * 0.02).to(torch.bfloat16)
+    Q = torch.randn(B, S_new, nh_q, 128, generator=g).to(torch.bfloat16)
+    S_total = S_past + S_new
+    K = torch.zeros(B, S_total, nh_kv, 128, dtype=torch.bfloat16)
+    V = torch.zeros(B, S_total, nh_kv, 128, dtype=torch.bfloat16)
+    std = 0.02 * H ** 0.5
+    K[:, :S_past] = (torch.randn(B, S_past, nh_kv, 128, generator=g) * std).to(torch.bfloat16)
+    V[:, :S_past] = (torch.randn(B, S_past, nh_kv, 128, generator=g) * std).to(torch.bfloat16)
+    cs = orc.build_cos_sin(S_total + 8, 128, 500000.0) if rope else None
+    return X, Wk, Wv, Q, K, V, cs
+
+
+@pytest.mark.parametrize("H", [64, 128, 1024, 4096, 7168])
+def test_projection_full_hidden_with_rope(H):
+    """The projection contracts ALL hidden columns (tcgen05, split-K) and rotates K at absolute positions."""
+    X, Wk, Wv, Q, K, V, cs = _rand_case(2, 8, 2, 40, 24, H, seed=100 + H)
+    _run_fwd(X, Wk, Wv, Q, K, V, cs, True, 24)
+
+
+@pytest.mark.parametrize("S_new,S_past", [(1, 0), (1, 333), (130, 0), (257, 70), (64, 64)])
+def test_unaligned_lengths_gqa(S_new, S_past):
+    X, Wk, Wv, Q, K, V, cs = _rand_case(2, 8, 2, S_new, S_past, 256, seed=7 + S_new)
+    _run_fwd(X, Wk, Wv, Q, K, V, cs, True, S_past)
+
+
+def test_many_token_tiles_no_split_k():
+    """More than one 128-token tile per head and enough tiles that split-K is off."""
+    X, Wk, Wv, Q, K, V, cs = _rand_case(1, 32, 32, 300, 0, 512, seed=55, rope=False)
+    _run_fwd(X, Wk, Wv, Q, K, V, cs, True, 0)
+
+
+def test_q_rotation_and_hbm_pool():
+    X, Wk, Wv, Q, K, V, cs = _rand_case(1, 4, 4, 48, 80, 128, seed=77)
+    _run_fwd(X, Wk, Wv, Q, K, V, cs, True, 80, q_pos_start=80, kv_on_host=False)
+
+
+def test_checks_match_reference_messages():
+    X, Wk, Wv, Q, K, V, cs = _rand_case(1, 4, 4, 16, 16, 128, seed=3, rope=False)
+    Xd, Wkd, Wvd, Qd = X.to(DEV), Wk.to(DEV), Wv.to(DEV), Q.to(DEV)
+    Kp, Vp = K.pin_memory(), V.pin_memory()
+    with pytest.raises(RuntimeError, match="S_total"):
+        kernel.smpv2_fwd(Xd, Wkd, Wvd, Qd, Kp, Vp, None, SCALE, True, 8, -1)
+    with pytest.raises(RuntimeError, match="bfloat16"):
+        kernel.smpv2_fwd(Xd.float(), Wkd, Wvd, Qd, Kp, Vp, None, SCALE, True, 16, -1)
+    with pytest.raises(RuntimeError, match="3D"):
+        kernel.smpv2_fwd(Xd[0], Wkd, Wvd, Qd, Kp, Vp, None, SCALE, True, 16, -1)
+    with pytest.raises(RuntimeError, match="multiple"):
+        kernel.smpv2_fwd(Xd, Wkd[:3].contiguous(), Wvd[:3].contiguous(), Qd, Kp[:, :, :3].contiguous().pin_memory(),
+                         Vp[:, :, :3].contiguous().pin_memory(), None, SCALE, True, 16, -1)
+    with pytest.raises(RuntimeError, match="not initialized"):
+        kernel.smpv2_fwd_graph(12345, Xd, Qd, torch.empty_like(Qd), torch.zeros(1, dtype=torch.int32, device=DEV),
+                               torch.zeros(1, dtype=torch.int32, device=DEV), None, SCALE, True, 64, 0)
+
+
+def test_graph_entry_points_replay():
+    """smpv2_init_tma + smpv2_fwd_graph: loop bounds come from device memory, pool rows from
+    req_pool_indices; captured once in a CUDA graph and replayed with a different past length."""
+    nh, H, S_new, rows, S_max = 4, 128, 64, 3, 256
+    g = torch.Generator().manual_seed(5)
+    Wk = (torch.randn(nh, 128, H, generator=g) * 0.05).to(torch.bfloat16)
+    Wv = (torch.randn(nh, 128, H, generator=g) * 0.05).to(torch.bfloat16)
+    K_pool = (torch.randn(rows, S_max, nh, 128, generator=g) * 0.3).to(torch.bfloat16).pin_memory()
+    V_pool = (torch.randn(rows, S_max, nh, 128, generator=g) * 0.3).to(torch.bfloat16).pin_memory()
+    bs = 2
+    X = torch.randn(bs, S_new, H, generator=g).to(torch.bfloat16).to(DEV)
+    Q = torch.randn(bs, S_new, nh, 128, generator=g).to(torch.bfloat16).to(DEV)
+    O = torch.empty_like(Q)
+    n_past = torch.zeros(1, dtype=torch.int32, device=DEV)
+    n_blks = torch.zeros(1, dtype=torch.int32, device=DEV)
+    rpi = torch.tensor([2, 0], dtype=torch.int32, device=DEV)
+    kernel.smpv2_init_tma(50, X, Wk.to(DEV), Wv.to(DEV), Q, K_pool, V_pool)
+
+    def oracle(past):
+        Kr, Vr = K_pool.clone(), V_pool.clone()
+        outs = []
+        for b, r in enumerate([2, 0]):
+            kb, vb = Kr[r:r + 1, :past + S_new].clone(), Vr[r:r + 1, :past + S_new].clone()
+            outs.append(orc.smpv2_fwd(X[b:b + 1].cpu(), Wk, Wv, Q[b:b + 1].cpu(), kb, vb, None, SCALE, True, past)[0])
+        return torch.stack(outs)
+
+    n_past.fill_(1)
+    ref1 = oracle(64)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        kernel.smpv2_fwd_graph(50, X, Q, O, n_past, n_blks, None, SCALE, True, S_max, S_max - 64, rpi)  # warm-up
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    assert_close(O, ref1, "eager O")
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        kernel.smpv2_fwd_graph(50, X, Q, O, n_past, n_blks, None, SCALE, True, S_max, S_max - 64, rpi)
+    n_past.fill_(2)
+    ref2 = oracle(128)
+    graph.replay()
+    torch.cuda.synchronize()
+    get_context(0).raise_on_status()
+    assert_close(O, ref2, "replayed O")
+    kernel.unregister_layer(50)
