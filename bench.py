@@ -1,0 +1,332 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-attention hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one decode step of one layer for one ragged batch (K/V projection of the new tokens on
+tensor cores + RoPE + write-back, split-KV attention streamed from the KV pool, LSE merge).
+Workload: the OPT-6.7B layer configuration (hidden 4096, 32 MHA heads, head_dim 128, no RoPE),
+16 requests with context lengths uniform in [512, 8192], 16-token pages, randomly permuted page
+table; seeded synthetic tensors (there are no model weights or traces on the machine).
+
+Reported on one JSON line:
+  value  - KV GB/s with the KV pool resident in HBM (inputs on the device before timing starts)
+  e2e    - the same metric through the public Python API with the KV pool in page-locked HOST
+           memory: the kernel streams it over PCIe inside the timed region, and every step also
+           copies X, Q and the lengths host->device from pinned memory and the output back.
+  roofline     - the KV-streaming kernel alone: algorithmic KV bytes per launch / its mean launch
+                 duration (CUDA events on the launching stream) against the measured HBM copy peak
+  cpu_baseline - the CPU restatement of the reference's torch path, timed on the host cores
+  clocks, gpu_launches, host_link (pinned host->device copy bandwidth measured in this run)
+With N > 1 (torchrun) every rank owns its own 32-head shard and its own host pool; there is no
+data-path collective (per-GPU work is fixed: weak scaling).
+
+--impl reference times the reference's torch attention path, restated for the CPU in fp32
+(oracle/), on the host cores for the same configuration.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from directkv_b200 import workloads  # noqa: E402
+
+CFG_ID = 1
+PAGE = 16
+METRIC = "decode_attention_kv_gbps"
+UNIT = "GB/s"
+
+
+def c2_lengths(rank: int = 0):
+    # +1: the token decoded in this step (its K/V are projected, stored and attended too)
+    return [n + 1 for n in workloads.ragged_lengths_uniform(16, 512, 8192, seed=4234 + CFG_ID + 97 * rank)]
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed regions run."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 9:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [x for x in sm if x > 0.5 * (max(mx) if mx else 1)] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_time(steps: int, warmup: int, lens, sample_idx):
+    """Times the reference's torch attention path (fp32, CPU) on a bounded sample of the workload."""
+    from oracle import directkv_oracle as orc
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    shape = workloads.OPT_6_7B
+    sub = [lens[i] for i in sample_idx]
+    case = workloads.make_decode_case(shape, sub, PAGE, CFG_ID, "cpu", kv_on_host=True)
+    args = (case["x"], case["wk"], case["wv"], case["q"], case["k_pool"], case["v_pool"], case["page_table"], sub,
+            PAGE, None, shape.scale)
+    for _ in range(warmup):
+        orc.decode_layer(*args)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        orc.decode_layer(*args)
+    dt = (time.perf_counter() - t0) / steps
+    nbytes = workloads.kv_bytes(shape, sub)
+    return nbytes / dt / 1e9, dt * 1e3, torch.get_num_threads(), f"{len(sub)} of {len(lens)} requests ({sum(sub)} tokens) per step"
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    lens = c2_lengths(0)
+    steps = max(1, min(args.steps, 10))
+    gbs, ms, cores, sample = cpu_reference_time(steps, max(1, min(args.warmup, 2)), lens, list(range(0, 16, 4)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "opt-6.7b layer decode, 16 ragged requests ctx U[512,8192], 16-token permuted pages",
+                   "note": "reference's torch attention path (gather by slot + scaled_dot_product_attention) "
+                           "restated in fp32 on the CPU; the reference's own kernel is sm_90a-only"},
+        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--variant", type=int, default=None, help="override the streaming-kernel variant")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    from directkv_b200 import kernel
+    from directkv_b200._lib import get_context
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+
+    def sum_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    shape = workloads.OPT_6_7B
+    lens = c2_lengths(rank)
+    ctx = get_context(local_rank)
+    if args.variant is not None:
+        ctx.set("attn_variant", args.variant)
+
+    # ---- inputs: one host-resident pool, one HBM-resident copy of it --------------------------------
+    case = workloads.make_decode_case(shape, lens, PAGE, CFG_ID + 100 * rank, dev, kv_on_host=True)
+    k_host, v_host = case["k_pool"], case["v_pool"]
+    k_hbm, v_hbm = k_host.to(dev), v_host.to(dev)
+    kernel.register_layer(0, k_host, v_host, case["wk"], case["wv"], None, page_size=PAGE, device=local_rank)
+    kernel.register_layer(1, k_hbm, v_hbm, case["wk"], case["wv"], None, page_size=PAGE, device=local_rank)
+    B = len(lens)
+    x_pin, q_pin = case["x"].cpu().pin_memory(), case["q"].cpu().pin_memory()
+    len_pin = case["seq_lens"].cpu().pin_memory()
+    x_dev, q_dev, len_dev = torch.empty_like(case["x"]), torch.empty_like(case["q"]), torch.empty_like(case["seq_lens"])
+    out_dev = torch.empty_like(case["q"])
+    out_pin = torch.empty(out_dev.shape, dtype=out_dev.dtype, pin_memory=True)
+    table = case["page_table"]
+    kv_total = workloads.kv_bytes(shape, lens)                       # every attended token, incl. the new one
+    kv_streamed = workloads.kv_bytes(shape, [n - 1 for n in lens])   # what the streaming kernel reads
+    kv_all_ranks = sum_over_ranks(float(kv_total))
+
+    def step_hbm():
+        kernel.decode(1, case["q"], case["seq_lens"], shape.scale, page_table=table, x=case["x"], out=out_dev)
+
+    def step_e2e():
+        x_dev.copy_(x_pin, non_blocking=True)
+        q_dev.copy_(q_pin, non_blocking=True)
+        len_dev.copy_(len_pin, non_blocking=True)
+        kernel.decode(0, q_dev, len_dev, shape.scale, page_table=table, x=x_dev, out=out_dev)
+        out_pin.copy_(out_dev, non_blocking=True)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)) / steps
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+
+    # ---- HBM-resident mode: `value` and the roofline of the streaming kernel -------------------------
+    for _ in range(args.warmup):
+        step_hbm()
+    ctx.profile_read(reset=True)
+    ctx.set("profile_attn", 1)
+    ms_hbm = timed(step_hbm, args.steps, 0)
+    attn_ms, attn_n, launches_hbm = ctx.profile_read(reset=True)
+    ctx.set("profile_attn", 0)
+    ctx.raise_on_status()
+
+    # ---- host-KV mode through the public API: `e2e` -----------------------------------------------------
+    e2e_steps = max(3, min(args.steps, 20))
+    ms_e2e = timed(step_e2e, e2e_steps, 3)
+    ctx.raise_on_status()
+
+    # ---- host link peak: pinned host->device copy of >= 1 GiB --------------------------------------
+    nb = 1 << 30
+    hbuf = torch.empty(nb, dtype=torch.uint8, pin_memory=True)
+    dbuf = torch.empty(nb, dtype=torch.uint8, device=dev)
+    best = 1e30
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        dbuf.copy_(hbuf, non_blocking=True)
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b))
+    link_gbs = nb / best / 1e6
+    del hbuf, dbuf
+
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peak, peak_kind = measured_peaks()
+    attn_avg_ms = attn_ms / max(attn_n, 1)
+    achieved = kv_streamed / attn_avg_ms / 1e6 if attn_avg_ms > 0 else 0.0
+    cpu_gbs, cpu_ms, cores, sample = cpu_reference_time(2, 1, lens, [0, 8]) if world == 1 else (None, None, None, None)
+
+    line = {
+        "metric": METRIC, "value": kv_all_ranks / ms_hbm / 1e6, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_hbm, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "opt-6.7b layer decode, 16 ragged requests ctx U[512,8192], 16-token permuted pages",
+                   "kv_bytes_per_step_per_gpu": kv_total, "tokens": sum(lens), "page_size": PAGE,
+                   "parallelism": f"head-shard x{world}: one 32-KV-head shard and one host pool per rank, no collective",
+                   "l2": "inputs larger than L2 (0.98 GB of KV per step vs 126 MB)",
+                   "value_mode": "KV pool resident in HBM", "e2e_mode": "KV pool in pinned host memory, streamed over PCIe"},
+        "e2e": {"value": kv_all_ranks / ms_e2e / 1e6, "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": kv_streamed + x_pin.numel() * 2 + q_pin.numel() * 2 + len_pin.numel() * 4,
+                "d2h_bytes_per_step": out_pin.numel() * 2 + B * shape.nh_kv * 2 * 128 * 2,
+                "steps": e2e_steps},
+        "host_link": {"peak_gbs": link_gbs, "how": "pinned host->device copy of 1 GiB, best of 5, this run",
+                      "achieved_gbs": kv_total / ms_e2e / 1e6, "frac": kv_total / ms_e2e / 1e6 / link_gbs},
+        "roofline": {"kernel": "attn_partial_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
+                     "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes": kv_streamed,
+                     "avg_launch_ms": attn_avg_ms, "launches_timed": attn_n},
+        "gpu_launches": launches_hbm,
+        "clocks": clocks,
+    }
+    if cpu_gbs is not None:
+        line["cpu_baseline"] = {"value": cpu_gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                "ms_per_step": cpu_ms}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) per launch of the streaming kernel from the ncu capture summarised in
+# profiles/; None until a capture of this workload exists.
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+if __name__ == "__main__":
+    main()

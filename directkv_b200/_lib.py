@@ -84,6 +84,8 @@ SIGNATURES = {
     "dkv_context_destroy": (C.c_int, [C.c_void_p]),
     "dkv_context_reserve": (C.c_int, [C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int]),
     "dkv_context_set": (C.c_int, [C.c_void_p, C.c_char_p, C.c_int]),
+    "dkv_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_longlong),
+                                   C.POINTER(C.c_longlong), C.c_int]),
     "dkv_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint), C.c_int]),
     "dkv_layer_register": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(LayerDesc)]),
     "dkv_layer_unregister": (C.c_int, [C.c_void_p, C.c_int]),
@@ -154,6 +156,12 @@ class Context:
         st = C.c_uint(0)
         check(load().dkv_read_status(self.handle, C.byref(st), 1 if clear else 0))
         return st.value
+
+    def profile_read(self, reset: bool = True):
+        """(summed ms of the bracketed streaming-kernel launches, their count, all launches)."""
+        ms, n, tot = C.c_double(0), C.c_longlong(0), C.c_longlong(0)
+        check(load().dkv_profile_read(self.handle, C.byref(ms), C.byref(n), C.byref(tot), 1 if reset else 0))
+        return ms.value, n.value, tot.value
 
     def raise_on_status(self) -> None:
         """Synchronises the device and raises if any kernel recorded a failure."""

@@ -10,6 +10,8 @@
 #include <cstring>
 #include <map>
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "dkv_attn.cuh"
 #include "dkv_proj.cuh"
@@ -114,6 +116,11 @@ struct dkv_context {
     int attn_variant = 0;
     int attn_ctas = 0;
     int proj_split_k = 0;
+    // Profiling: kernel launches issued, and CUDA-event pairs around the streaming kernel.
+    long long launches = 0;
+    int profile_attn = 0;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> attn_events;
+    size_t attn_events_used = 0;
 };
 
 namespace {
@@ -406,6 +413,7 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
     dim3 grid(L.d.nh_kv, (T + kProjBM - 1) / kProjBM, pp.split_k);
     proj_rope_kernel<kProjStages><<<grid, 128, kProjSmem, st>>>(tmX, L.tmWk, L.tmWv, pp);
     DKV_CUDA(cudaGetLastError());
+    ctx->launches += 1;
     return DKV_OK;
 }
 
@@ -418,10 +426,23 @@ int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool
     const CUtensorMap& tmK = paged ? L.tmK_page : L.tmK_16;
     const CUtensorMap& tmV = paged ? L.tmV_page : L.tmV_16;
     cudaError_t e;
+    std::pair<cudaEvent_t, cudaEvent_t>* ev = nullptr;
+    if (ctx->profile_attn) {
+        if (ctx->attn_events_used == ctx->attn_events.size() && ctx->attn_events.size() < 8192) {
+            cudaEvent_t a, b;
+            DKV_CUDA(cudaEventCreate(&a));
+            DKV_CUDA(cudaEventCreate(&b));
+            ctx->attn_events.emplace_back(a, b);
+        }
+        if (ctx->attn_events_used < ctx->attn_events.size()) ev = &ctx->attn_events[ctx->attn_events_used++];
+    }
+    if (ev) DKV_CUDA(cudaEventRecord(ev->first, st));
     if (G == 4) e = attn_dispatch<4>(ctx->attn_variant, ctas, tmK, tmV, ap, st);
     else if (G == 2) e = attn_dispatch<2>(ctx->attn_variant, ctas, tmK, tmV, ap, st);
     else e = attn_dispatch<1>(ctx->attn_variant, ctas, tmK, tmV, ap, st);
     DKV_CUDA(e);
+    if (ev) DKV_CUDA(cudaEventRecord(ev->second, st));
+    ctx->launches += 2;  // streaming kernel + merge
     MergeParams mp = mp_in;
     mp.a = ap;
     mp.G = G;
@@ -484,6 +505,10 @@ int dkv_context_destroy(dkv_context* ctx) {
     if (!ctx) return DKV_OK;
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
+    for (auto& ev : ctx->attn_events) {
+        cudaEventDestroy(ev.first);
+        cudaEventDestroy(ev.second);
+    }
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->counters) cudaFree(ctx->counters);
@@ -507,6 +532,8 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "attn_ctas")) {
         DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
         ctx->attn_ctas = value;
+    } else if (!strcmp(key, "profile_attn")) {
+        ctx->profile_attn = value ? 1 : 0;
     } else if (!strcmp(key, "proj_split_k")) {
         DKV_REQUIRE(value >= 0 && value <= 256, "proj_split_k out of range");
         ctx->proj_split_k = value;
@@ -524,6 +551,27 @@ int dkv_read_status(dkv_context* ctx, unsigned int* status, int clear) {
     if (clear && *status != 0) {
         DKV_CUDA(cudaMemset(ctx->status, 0, sizeof(unsigned int)));
         DKV_CUDA(cudaMemset(ctx->counters, 0, kMaxCounters * sizeof(unsigned int)));
+    }
+    return DKV_OK;
+}
+
+int dkv_profile_read(dkv_context* ctx, double* attn_ms_total, long long* attn_launches, long long* total_launches,
+                     int reset) {
+    DKV_REQUIRE(ctx != nullptr, "ctx is NULL");
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    DKV_CUDA(cudaDeviceSynchronize());
+    double ms = 0.0;
+    for (size_t i = 0; i < ctx->attn_events_used; ++i) {
+        float t = 0.f;
+        DKV_CUDA(cudaEventElapsedTime(&t, ctx->attn_events[i].first, ctx->attn_events[i].second));
+        ms += t;
+    }
+    if (attn_ms_total) *attn_ms_total = ms;
+    if (attn_launches) *attn_launches = static_cast<long long>(ctx->attn_events_used);
+    if (total_launches) *total_launches = ctx->launches;
+    if (reset) {
+        ctx->attn_events_used = 0;
+        ctx->launches = 0;
     }
     return DKV_OK;
 }
@@ -588,6 +636,7 @@ int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) {
 
     attn_prep_kernel<<<1, 256, 0, st>>>(a->seq_lens, a->batch, n_new, cum);
     DKV_CUDA(cudaGetLastError());
+    ctx->launches += 1 + (n_new ? 1 : 0) + (a->new_mode == DKV_NEW_GIVEN ? 1 : 0);
     if (n_new) {
         decode_newtok_kernel<<<(a->batch + 127) / 128, 128, 0, st>>>(a->seq_lens, a->page_table, a->pt_stride, a->row_map,
                                                                      a->batch, L.d.page_size, L.page_shift,
@@ -669,6 +718,7 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
     DKV_CUDA(cudaGetLastError());
     attn_prep_kernel<<<1, 256, 0, st>>>(vseq, static_cast<int>(rows), 0, cum);
     DKV_CUDA(cudaGetLastError());
+    ctx->launches += 2;
     rc = launch_projection(ctx, L, X, static_cast<int>(rows), tok_pos, tok_slot, true, nullptr,
                            reinterpret_cast<float*>(base + sp.splitk), st);
     if (rc != DKV_OK) return rc;

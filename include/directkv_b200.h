@@ -64,9 +64,18 @@ int dkv_context_destroy(dkv_context* ctx);
  */
 int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv, int hidden);
 
-/* Tuning knobs, by name: "attn_variant" (0..2), "attn_ctas" (CTAs of the streaming kernel,
- * 0 = one per SM), "proj_split_k" (0 = automatic). */
+/* Knobs, by name: "attn_variant" (0..2), "attn_ctas" (CTAs of the streaming kernel,
+ * 0 = one per SM), "proj_split_k" (0 = automatic), "profile_attn" (0/1, see dkv_profile_read). */
 int dkv_context_set(dkv_context* ctx, const char* key, int value);
+
+/*
+ * Profiling counters.  With dkv_context_set(ctx, "profile_attn", 1) every launch of the
+ * KV-streaming kernel is bracketed by CUDA events on the stream it is launched on;
+ * this call synchronises the device and returns their summed duration, how many launches
+ * were bracketed, and how many kernels the context has launched in total since the last reset.
+ */
+int dkv_profile_read(dkv_context* ctx, double* attn_ms_total, long long* attn_launches, long long* total_launches,
+                     int reset);
 
 /* Blocks until the stream work touching the status word is done is NOT implied: this
  * synchronises the device, copies the status word and optionally clears it. */
