@@ -162,6 +162,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--variant", type=int, default=None, help="override the streaming-kernel variant")
+    ap.add_argument("--only", default="all", choices=["all", "hbm"],
+                    help="hbm: time only the HBM-resident mode (short run for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -262,6 +264,15 @@ def main():
     attn_ms, attn_n, launches_hbm = ctx.profile_read(reset=True)
     ctx.set("profile_attn", 0)
     ctx.raise_on_status()
+
+    if args.only == "hbm":
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"metric": METRIC, "value": kv_all_ranks / ms_hbm / 1e6, "unit": UNIT,
+                              "ms_per_step": ms_hbm, "attn_avg_ms": attn_ms / max(attn_n, 1), "partial": "hbm only"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- host-KV mode through the public API: `e2e` -----------------------------------------------------
     e2e_steps = max(3, min(args.steps, 20))

@@ -50,21 +50,52 @@ struct AttnParams {
 };
 
 // ---------------------------------------------------------------------------
-// prep: tiles per request -> exclusive prefix sum.  One CTA.
+// prep: tiles per request -> exclusive prefix sum; with n_new == 1 also the position and the
+// destination slot of the token each request adds in this step.  One CTA.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) attn_prep_kernel(const int* __restrict__ seq_lens, int batch, int n_new,
-                                                        int* __restrict__ cum_tiles) {
+struct PrepParams {
+    const int* seq_lens;
+    int batch;
+    int n_new;
+    int* cum_tiles;           // [batch + 1]
+    // new-token bookkeeping (n_new == 1), any of these may be nullptr
+    int* tok_pos;             // [batch] seq_len - 1
+    int* tok_slot;            // [batch] slot the token is stored to, or -1
+    const int* page_table;
+    const int* row_map;
+    int pt_stride, page_size, page_shift;
+    long long row_stride;
+    int save;
+};
+
+__global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams pp) {
     __shared__ int warp_tot[8];
     __shared__ int carry_s;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (tid == 0) carry_s = 0;
     __syncthreads();
-    for (int base = 0; base < batch; base += 256) {
+    for (int base = 0; base < pp.batch; base += 256) {
         const int b = base + tid;
         int v = 0;
-        if (b < batch) {
-            int past = seq_lens[b] - n_new;
+        if (b < pp.batch) {
+            const int len = pp.seq_lens[b];
+            const int past = len - pp.n_new;
             v = past > 0 ? (past + kTileTokens - 1) / kTileTokens : 0;
+            if (pp.n_new && pp.tok_pos != nullptr) {
+                const int pos = len - 1;
+                long long slot = -1;
+                if (pp.save && pos >= 0) {
+                    const int row = pp.row_map ? pp.row_map[b] : b;
+                    if (pp.page_table)
+                        slot = (static_cast<long long>(
+                                    pp.page_table[static_cast<long long>(row) * pp.pt_stride + (pos >> pp.page_shift)])
+                                << pp.page_shift) + (pos & (pp.page_size - 1));
+                    else
+                        slot = static_cast<long long>(row) * pp.row_stride + pos;
+                }
+                pp.tok_pos[b] = pos;
+                pp.tok_slot[b] = static_cast<int>(slot);
+            }
         }
         int x = v;
 #pragma unroll
@@ -77,12 +108,12 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const int* __restrict__ 
         int woff = 0;
         for (int w = 0; w < warp; ++w) woff += warp_tot[w];
         const int carry = carry_s;
-        if (b < batch) cum_tiles[b] = carry + woff + x - v;
+        if (b < pp.batch) pp.cum_tiles[b] = carry + woff + x - v;
         __syncthreads();
         if (tid == 255) carry_s = carry + woff + x;
         __syncthreads();
     }
-    if (tid == 0) cum_tiles[batch] = carry_s;
+    if (tid == 0) pp.cum_tiles[pp.batch] = carry_s;
 }
 
 // ---------------------------------------------------------------------------

@@ -113,7 +113,9 @@ struct dkv_context {
     unsigned int* status = nullptr;     // device status word
     unsigned int* counters = nullptr;   // split-K arrival counters, zero between launches
     std::map<int, LayerState> layers;
-    int attn_variant = 0;
+    cudaStream_t side = nullptr;        // projection overlaps the streamed attention here
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    int attn_variant = -1;              // -1: chosen per call from the head grouping
     int attn_ctas = 0;
     int proj_split_k = 0;
     // Profiling: kernel launches issued, and CUDA-event pairs around the streaming kernel.
@@ -128,27 +130,6 @@ namespace {
 // ---------------------------------------------------------------------------
 // Small kernels that live with the host logic
 // ---------------------------------------------------------------------------
-
-// Decode: position and destination slot of the token each request adds in this step.
-__global__ void decode_newtok_kernel(const int* __restrict__ seq_lens, const int* __restrict__ page_table,
-                                     int pt_stride, const int* __restrict__ row_map, int batch, int page_size,
-                                     int page_shift, long long row_stride, int save, int* __restrict__ tok_pos,
-                                     int* __restrict__ tok_slot) {
-    const int b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= batch) return;
-    const int pos = seq_lens[b] - 1;
-    tok_pos[b] = pos;
-    long long slot = -1;
-    if (save && pos >= 0) {
-        const int row = row_map ? row_map[b] : b;
-        if (page_table)
-            slot = (static_cast<long long>(page_table[static_cast<long long>(row) * pt_stride + (pos >> page_shift)])
-                    << page_shift) + (pos & (page_size - 1));
-        else
-            slot = static_cast<long long>(row) * row_stride + pos;
-    }
-    tok_slot[b] = static_cast<int>(slot);
-}
 
 // Extend: every new row becomes a virtual request that attends past + its causal prefix.
 __global__ void extend_prep_kernel(int B, int S_new, int seqlen_past_host, const int* __restrict__ n_past_blocks_dev,
@@ -272,7 +253,9 @@ cudaError_t attn_dispatch(int variant, int ctas, const CUtensorMap& tmK, const C
 }
 
 constexpr int kProjStages = 4;
-constexpr size_t kProjSmem = static_cast<size_t>(kProjStages) * kProjStage + 1024 /*control*/ + 1024 /*alignment*/;
+// stages | control (barriers, TMEM holder) | alignment slack; the epilogue re-uses the stage area for
+// the split-K sum tile (128 x 260 floats) followed by the 64 KB bf16 output staging tile.
+constexpr size_t kProjSmem = static_cast<size_t>(kProjStages) * kProjStage + 4096 + 1024 + 1024;
 
 size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
@@ -282,11 +265,16 @@ struct ScratchPlan {
 
 int choose_g(int g_total) { return (g_total % 4 == 0) ? 4 : (g_total % 2 == 0) ? 2 : 1; }
 
-int variant_warps(const dkv_context* ctx, int G) {
+// Variant actually launched for a head grouping: 16 warps x 1 stage measured best for G <= 2;
+// G == 4 needs more registers per thread and runs 8 warps x 3 stages unless overridden.
+int effective_variant(const dkv_context* ctx, int G) {
     int v = ctx->attn_variant;
+    if (v < 0) v = (G <= 2) ? 2 : 0;
     if (v == 2 && G > 2) v = 1;
-    return kVarWarps[v];
+    return v;
 }
+
+int variant_warps(const dkv_context* ctx, int G) { return kVarWarps[effective_variant(ctx, G)]; }
 
 int attn_cta_count(const dkv_context* ctx) { return ctx->attn_ctas > 0 ? ctx->attn_ctas : ctx->sm_count; }
 
@@ -418,7 +406,7 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
 }
 
 int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool paged, const MergeParams& mp_in,
-                     cudaStream_t st) {
+                     cudaStream_t st, cudaEvent_t join_before_merge = nullptr) {
     const int G = choose_g(ap.g_total);
     ap.nsub = ap.g_total / G;
     const int ctas = attn_cta_count(ctx);
@@ -437,12 +425,13 @@ int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool
         if (ctx->attn_events_used < ctx->attn_events.size()) ev = &ctx->attn_events[ctx->attn_events_used++];
     }
     if (ev) DKV_CUDA(cudaEventRecord(ev->first, st));
-    if (G == 4) e = attn_dispatch<4>(ctx->attn_variant, ctas, tmK, tmV, ap, st);
-    else if (G == 2) e = attn_dispatch<2>(ctx->attn_variant, ctas, tmK, tmV, ap, st);
-    else e = attn_dispatch<1>(ctx->attn_variant, ctas, tmK, tmV, ap, st);
+    if (G == 4) e = attn_dispatch<4>(effective_variant(ctx, 4), ctas, tmK, tmV, ap, st);
+    else if (G == 2) e = attn_dispatch<2>(effective_variant(ctx, 2), ctas, tmK, tmV, ap, st);
+    else e = attn_dispatch<1>(effective_variant(ctx, 1), ctas, tmK, tmV, ap, st);
     DKV_CUDA(e);
     if (ev) DKV_CUDA(cudaEventRecord(ev->second, st));
     ctx->launches += 2;  // streaming kernel + merge
+    if (join_before_merge) DKV_CUDA(cudaStreamWaitEvent(st, join_before_merge, 0));
     MergeParams mp = mp_in;
     mp.a = ap;
     mp.G = G;
@@ -482,6 +471,9 @@ int dkv_context_create(int device, dkv_context** out) {
     if (e == cudaSuccess) e = cudaMemset(ctx->status, 0, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->counters, kMaxCounters * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(ctx->counters, 0, kMaxCounters * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->side, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming);
     if (e == cudaSuccess) e = attn_set_attr<1, 8, 3>();
     if (e == cudaSuccess) e = attn_set_attr<2, 8, 3>();
     if (e == cudaSuccess) e = attn_set_attr<4, 8, 3>();
@@ -509,6 +501,9 @@ int dkv_context_destroy(dkv_context* ctx) {
         cudaEventDestroy(ev.first);
         cudaEventDestroy(ev.second);
     }
+    if (ctx->side) cudaStreamDestroy(ctx->side);
+    if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+    if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->counters) cudaFree(ctx->counters);
@@ -527,7 +522,7 @@ int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv,
 int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     DKV_REQUIRE(ctx != nullptr && key != nullptr, "ctx / key is NULL");
     if (!strcmp(key, "attn_variant")) {
-        DKV_REQUIRE(value >= 0 && value <= 2, "attn_variant must be 0..2");
+        DKV_REQUIRE(value >= -1 && value <= 2, "attn_variant must be -1 (automatic) or 0..2");
         ctx->attn_variant = value;
     } else if (!strcmp(key, "attn_ctas")) {
         DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
@@ -634,19 +629,32 @@ int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) {
     __nv_bfloat16* kv_new = reinterpret_cast<__nv_bfloat16*>(base + sp.kv_new);
     const int n_new = a->new_mode == DKV_NEW_NONE ? 0 : 1;
 
-    attn_prep_kernel<<<1, 256, 0, st>>>(a->seq_lens, a->batch, n_new, cum);
+    PrepParams prep{};
+    prep.seq_lens = a->seq_lens;
+    prep.batch = a->batch;
+    prep.n_new = n_new;
+    prep.cum_tiles = cum;
+    prep.tok_pos = tok_pos;
+    prep.tok_slot = tok_slot;
+    prep.page_table = a->page_table;
+    prep.row_map = a->row_map;
+    prep.pt_stride = a->pt_stride;
+    prep.page_size = L.d.page_size;
+    prep.page_shift = L.page_shift;
+    prep.row_stride = L.d.row_stride;
+    prep.save = a->save_kv_cache;
+    attn_prep_kernel<<<1, 256, 0, st>>>(prep);
     DKV_CUDA(cudaGetLastError());
-    ctx->launches += 1 + (n_new ? 1 : 0) + (a->new_mode == DKV_NEW_GIVEN ? 1 : 0);
-    if (n_new) {
-        decode_newtok_kernel<<<(a->batch + 127) / 128, 128, 0, st>>>(a->seq_lens, a->page_table, a->pt_stride, a->row_map,
-                                                                     a->batch, L.d.page_size, L.page_shift,
-                                                                     L.d.row_stride, a->save_kv_cache, tok_pos, tok_slot);
-        DKV_CUDA(cudaGetLastError());
-    }
+    ctx->launches += 1 + (a->new_mode == DKV_NEW_GIVEN ? 1 : 0);
     if (a->new_mode == DKV_NEW_PROJECT) {
+        // The projection does not depend on the streamed attention: it runs on the context's side
+        // stream (forked after prep, joined before the merge) so the two overlap.
+        DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
+        DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
         rc = launch_projection(ctx, L, a->x, a->batch, tok_pos, tok_slot, a->save_kv_cache != 0, kv_new,
-                               reinterpret_cast<float*>(base + sp.splitk), st);
+                               reinterpret_cast<float*>(base + sp.splitk), ctx->side);
         if (rc != DKV_OK) return rc;
+        DKV_CUDA(cudaEventRecord(ctx->ev_join, ctx->side));
     } else if (a->new_mode == DKV_NEW_GIVEN) {
         const long long warps = static_cast<long long>(a->batch) * nh_kv;
         store_new_kv_kernel<<<static_cast<int>((warps + 3) / 4), 128, 0, st>>>(
@@ -682,7 +690,7 @@ int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) {
     mp.out_stride = a->out_stride;
     mp.lse = a->lse_out;
     mp.part_out = a->partial_out;
-    return launch_attention(ctx, L, ap, paged, mp, st);
+    return launch_attention(ctx, L, ap, paged, mp, st, a->new_mode == DKV_NEW_PROJECT ? ctx->ev_join : nullptr);
 }
 
 int dkv_merge_partials(dkv_context* ctx, const float* parts, int nranks, int64_t rows, void* out, float* lse,
@@ -716,7 +724,12 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
     extend_prep_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, st>>>(
         B, S_new, seqlen_past, n_past_blocks_dev, is_causal, row_map, L.d.row_stride, vseq, vrow, tok_pos, tok_slot);
     DKV_CUDA(cudaGetLastError());
-    attn_prep_kernel<<<1, 256, 0, st>>>(vseq, static_cast<int>(rows), 0, cum);
+    PrepParams prep{};
+    prep.seq_lens = vseq;
+    prep.batch = static_cast<int>(rows);
+    prep.n_new = 0;
+    prep.cum_tiles = cum;
+    attn_prep_kernel<<<1, 256, 0, st>>>(prep);
     DKV_CUDA(cudaGetLastError());
     ctx->launches += 2;
     rc = launch_projection(ctx, L, X, static_cast<int>(rows), tok_pos, tok_slot, true, nullptr,

@@ -25,6 +25,7 @@ constexpr int kProjABytes    = kProjBM * kProjBK * 2; // 16 KB
 constexpr int kProjBBytes    = kProjBN * kProjBK * 2; // 32 KB
 constexpr int kProjStage     = kProjABytes + kProjBBytes;
 constexpr int kProjTmemCols  = 256;
+constexpr int kProjAccStride = kProjBN + 4;           // floats between rows of the split-K sum tile
 constexpr int kProjHead      = 128;                   // head dimension (rows of Wk_h / Wv_h)
 
 struct ProjParams {
@@ -53,7 +54,9 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // The swizzled operand tiles need 1024-byte alignment.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* ctrl = smem + NST * kProjStage;
+    // Control words sit behind the area the epilogue re-uses (sum tile + output staging = 198,656 B).
+    uint8_t* ctrl = smem + NST * kProjStage + 4096;
+    static_assert(NST * kProjStage + 4096 >= kProjBM * kProjAccStride * 4 + kProjBM * 512, "epilogue tiles overlap the control words");
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
     uint64_t* empty_bar = full_bar + NST;
     uint64_t* accum_bar = empty_bar + NST;
@@ -151,7 +154,7 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const int row = warp * 32 + lane;
     const int token = mt * kProjBM + row;
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    uint8_t* stage_out = smem;  // [128 rows][512 B], 16-byte chunks XOR-swizzled by row
+    uint8_t* stage_out = smem;  // [128 rows][512 B], 16-byte chunks XOR-swizzled by row (after the sum tile with split-K)
     bool finalize = !aborted;
 
     if (!aborted && p.split_k > 1) {
@@ -183,14 +186,35 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         if (finalize) __threadfence();
     }
 
+    // Split-K: all threads of the last CTA add the slices (fixed order s = 0, 1, ...) into an fp32
+    // tile in shared memory; rows are 260 floats apart so that the row-per-thread reads below do not
+    // collide on banks.
+    float* sacc = reinterpret_cast<float*>(smem);
+    if (finalize && p.split_k > 1) {
+        const int rows_valid = (p.T - mt * kProjBM) < kProjBM ? (p.T - mt * kProjBM) : kProjBM;
+        const float* tile0 = p.splitk_scratch + ((static_cast<size_t>(mt)) * p.nh_kv + h) * (kProjBM * kProjBN);
+        const size_t slice_stride = static_cast<size_t>(gridDim.y) * p.nh_kv * (kProjBM * kProjBN);
+        for (int idx = tid; idx < rows_valid * (kProjBN / 4); idx += 128) {
+            const int r = idx / (kProjBN / 4), c4 = idx % (kProjBN / 4);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s2 = 0; s2 < p.split_k; ++s2) {
+                const float4 f = __ldcg(reinterpret_cast<const float4*>(tile0 + s2 * slice_stride + r * kProjBN + c4 * 4));
+                acc.x += f.x;
+                acc.y += f.y;
+                acc.z += f.z;
+                acc.w += f.w;
+            }
+            *reinterpret_cast<float4*>(sacc + r * kProjAccStride + c4 * 4) = acc;
+        }
+        stage_out = smem + kProjBM * kProjAccStride * 4;
+        __syncthreads();
+    }
+
     // tcgen05.ld is warp-collective: a warp takes this branch as a whole (the condition is
     // warp-uniform) and lanes past the last token only skip the global-memory accesses.
     const bool warp_has_tokens = (mt * kProjBM + warp * 32) < p.T;
     const bool lane_valid = token < p.T;
     if (finalize && warp_has_tokens) {
-        const float* slice0 = p.splitk_scratch + ((static_cast<size_t>(mt)) * p.nh_kv + h) * (kProjBM * kProjBN) +
-                              static_cast<size_t>(row) * kProjBN;
-        const size_t slice_stride = static_cast<size_t>(gridDim.y) * p.nh_kv * (kProjBM * kProjBN);
         auto load32 = [&](int col, float (&v)[32]) {
             if (p.split_k == 1) {
                 uint32_t r[32];
@@ -199,18 +223,14 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
             } else {
+                const float* src = sacc + row * kProjAccStride + col;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = 0.f;
-                for (int s = 0; s < p.split_k; ++s) {
-                    const float* src = slice0 + s * slice_stride + col;
-#pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const float4 f = __ldcg(reinterpret_cast<const float4*>(src + i));
-                        v[i] += f.x;
-                        v[i + 1] += f.y;
-                        v[i + 2] += f.z;
-                        v[i + 3] += f.w;
-                    }
+                for (int i = 0; i < 32; i += 4) {
+                    const float4 f = *reinterpret_cast<const float4*>(src + i);
+                    v[i] = f.x;
+                    v[i + 1] = f.y;
+                    v[i + 2] = f.z;
+                    v[i + 3] = f.w;
                 }
             }
         };

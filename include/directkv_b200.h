@@ -64,7 +64,7 @@ int dkv_context_destroy(dkv_context* ctx);
  */
 int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv, int hidden);
 
-/* Knobs, by name: "attn_variant" (0..2), "attn_ctas" (CTAs of the streaming kernel,
+/* Knobs, by name: "attn_variant" (-1 = automatic, 0..2), "attn_ctas" (CTAs of the streaming kernel,
  * 0 = one per SM), "proj_split_k" (0 = automatic), "profile_attn" (0/1, see dkv_profile_read). */
 int dkv_context_set(dkv_context* ctx, const char* key, int value);
 

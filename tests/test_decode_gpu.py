@@ -19,7 +19,7 @@ def _shape(hidden, nh_q, nh_kv, rope=True):
     return workloads.LayerShape(f"t{hidden}-{nh_q}-{nh_kv}", hidden, nh_q, nh_kv, 10000.0 if rope else None)
 
 
-def _run_decode(shape, seq_lens, page_size, cfg_id, kv_on_host=True, mode="project", variant=0, lid=7):
+def _run_decode(shape, seq_lens, page_size, cfg_id, kv_on_host=True, mode="project", variant=-1, lid=7):
     case = workloads.make_decode_case(shape, seq_lens, page_size, cfg_id, DEV, kv_on_host=kv_on_host)
     k_ref, v_ref = case["k_pool"].cpu().clone(), case["v_pool"].cpu().clone()
     k_before = k_ref.clone()
@@ -44,7 +44,7 @@ def _run_decode(shape, seq_lens, page_size, cfg_id, kv_on_host=True, mode="proje
     out = kernel.decode(lid, case["q"], case["seq_lens"], shape.scale, page_table=case["page_table"], **kw)
     ctx.raise_on_status()
     assert_close(out, ref.view_as(out), "O")
-    ctx.set("attn_variant", 0)
+    ctx.set("attn_variant", -1)
     if mode != "none":
         # Stored K/V of the new token: within the reference's write-back threshold; every other slot untouched.
         k_now, v_now = case["k_pool"].cpu(), case["v_pool"].cpu()
