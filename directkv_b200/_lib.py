@@ -76,6 +76,30 @@ class DecodeArgs(C.Structure):
     ]
 
 
+class NoAllocArgs(C.Structure):
+    _fields_ = [
+        ("k_pool", C.c_void_p),
+        ("v_pool", C.c_void_p),
+        ("n_slots", C.c_int64),
+        ("nh_kv", C.c_int),
+        ("page_size", C.c_int),
+        ("batch", C.c_int),
+        ("nh_q", C.c_int),
+        ("q", C.c_void_p),
+        ("q_stride", C.c_int64),
+        ("out", C.c_void_p),
+        ("out_stride", C.c_int64),
+        ("seq_lens", C.c_void_p),
+        ("page_table", C.c_void_p),
+        ("pt_stride", C.c_int),
+        ("softmax_scale", C.c_float),
+        ("lse_out", C.c_void_p),
+        ("sync_and_check", C.c_int),
+        ("err_buf", C.c_char_p),
+        ("err_buf_len", C.c_int),
+    ]
+
+
 # name -> (restype, argtypes); also the list of symbols include/directkv_b200.h declares.
 SIGNATURES = {
     "dkv_version": (C.c_int, []),
@@ -99,6 +123,7 @@ SIGNATURES = {
                              C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "dkv_scatter_kv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                  C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "dkv_decode_noalloc": (C.c_int, [C.POINTER(NoAllocArgs), C.c_void_p]),
     "dkv_stream_copy": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
 }
 

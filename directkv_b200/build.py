@@ -36,7 +36,7 @@ def find_nvcc() -> str:
 
 
 def sources():
-    return [CSRC / "dkv_capi.cu"]
+    return [CSRC / "dkv_capi.cu", CSRC / "dkv_noalloc.cu"]
 
 
 def headers():

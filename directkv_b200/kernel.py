@@ -200,6 +200,54 @@ def extend(
     return out
 
 
+def decode_noalloc(
+    k_pool: torch.Tensor,        # [n_slots, NH_kv, 128] bf16, pinned CPU or CUDA
+    v_pool: torch.Tensor,
+    q: torch.Tensor,             # [B, NH_q, 128] or [B, NH_q*128] bf16 CUDA
+    out: torch.Tensor,           # same shape as q, pre-allocated by the caller
+    seq_lens: torch.Tensor,      # [B] int32 CUDA; every attended token is already in the pool
+    page_table: torch.Tensor,    # [B, max_pages] int32 CUDA
+    page_size: int,
+    softmax_scale: float,
+    lse_out: Optional[torch.Tensor] = None,
+    sync_and_check: bool = False,
+) -> torch.Tensor:
+    """Attention-only decode that allocates no device memory (``dkv_decode_noalloc``).
+
+    For callers that cannot allocate when they call in: graph-capture regions, serving loops with
+    a frozen memory plan, hosts that forbid ``cudaMalloc`` from plugins.  The caller passes every
+    tensor, output included; scratch is a fixed 4 MiB array inside the library, shared by all
+    calls, so calls that overlap on the GPU race and sizes beyond the array are rejected with
+    ``RuntimeError``.  The first call on a device does a one-time set-up and should happen
+    before any stream capture.  Needs no registered layer and no context.
+    """
+    _check_kv(k_pool, "k_pool")
+    _check_kv(v_pool, "v_pool")
+    _check_cuda_bf16(q, "q")
+    _check_cuda_bf16(out, "out")
+    _chk(out.shape == q.shape, "out must have q's shape")
+    _chk(k_pool.dim() >= 3 and k_pool.size(-1) == HEAD_DIM and k_pool.shape == v_pool.shape, "pools must be [..., NH_kv, 128]")
+    b = q.size(0)
+    nh_q = q.numel() // (b * HEAD_DIM)
+    nh_kv = k_pool.size(-2)
+    _chk(seq_lens.is_cuda and seq_lens.dtype == torch.int32 and seq_lens.numel() == b, "seq_lens must be [B] int32 CUDA")
+    _chk(page_table.is_cuda and page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1,
+         "page_table must be 2D int32 CUDA with unit inner stride")
+    err = C.create_string_buffer(512)
+    a = _lib.NoAllocArgs(
+        k_pool=_ptr(k_pool), v_pool=_ptr(v_pool), n_slots=k_pool.numel() // (nh_kv * HEAD_DIM), nh_kv=nh_kv,
+        page_size=int(page_size), batch=b, nh_q=nh_q, q=_ptr(q), q_stride=nh_q * HEAD_DIM, out=_ptr(out),
+        out_stride=nh_q * HEAD_DIM, seq_lens=_ptr(seq_lens), page_table=_ptr(page_table),
+        pt_stride=page_table.stride(0), softmax_scale=float(softmax_scale), lse_out=_ptr(lse_out),
+        sync_and_check=1 if sync_and_check else 0, err_buf=C.cast(err, C.c_char_p), err_buf_len=512,
+    )
+    with torch.cuda.device(q.device):
+        rc = _lib.load().dkv_decode_noalloc(C.byref(a), _stream())
+    if rc != _lib.DKV_OK:
+        raise RuntimeError(f"directkv_b200 error {rc}: {err.value.decode()}")
+    return out
+
+
 def merge_partials(parts: torch.Tensor, out: Optional[torch.Tensor] = None,
                    lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Combines ``parts [R, rows, 132]`` (one unnormalised partial set per rank) into ``[rows, 128]`` bf16."""

@@ -194,6 +194,57 @@ int dkv_scatter_kv(dkv_context* ctx, void* k_pool, void* v_pool, int64_t n_slots
                    int64_t v_row_bytes, const void* loc, int loc_is_int64, const void* cache_k, const void* cache_v,
                    int64_t n_tokens, void* stream);
 
+/*
+ * Decode attention that allocates nothing.  It has no counterpart in the reference: it exists
+ * for callers that may not allocate device memory when they call in - code running during
+ * CUDA-graph capture, serving loops whose memory plan is frozen after start-up (all free HBM
+ * already belongs to the KV-cache allocator), and host processes that forbid cudaMalloc /
+ * cudaFree from plugins because those calls synchronise the device.  It needs no dkv_context:
+ * its scratch is a fixed 4 MiB array inside the library (present on every GPU that loads the
+ * library, for the life of the process).
+ *
+ * It computes what dkv_decode computes with new_mode == DKV_NEW_NONE over a paged pool: every
+ * attended token is already in the pool; out[b] = softmax(q[b] K^T * scale) V per head.
+ *
+ * Limits and rules
+ *  - sizes: batch <= 1983 and
+ *      (SMs * W + batch * nh_kv * nsub) * G * 528 bytes <= 4 MiB - 8 KiB,
+ *    with G = 4, 2 or 1 query heads handled together (the largest that divides nh_q / nh_kv),
+ *    nsub = (nh_q / nh_kv) / G and W = 8 warps for G == 4, else 16.  On a 148-SM B200 that is,
+ *    for example, 32 MHA heads up to batch 173, or Llama-3-8B's 32:8 GQA up to batch 99.  Larger
+ *    sizes are rejected with DKV_ERR_UNSUPPORTED and a message that names both byte counts.
+ *  - the first call on a device looks up the scratch array's device address and raises the
+ *    kernels' shared-memory limit; make that call before any stream capture begins.
+ *  - all calls share the one scratch array, which keeps the previous call's contents (the call
+ *    clears the status word it needs at zero itself).  Calls that overlap on the GPU race:
+ *    keep them on one stream or order them with events.
+ *  - errors: the message is written to err_buf (when given); dkv_last_error() is not used.
+ *  - the device uses the current device (cudaGetDevice) and the given stream.
+ */
+typedef struct {
+    void*          k_pool;        /* [n_slots, nh_kv, 128] bf16; host-pinned or device */
+    void*          v_pool;
+    int64_t        n_slots;
+    int            nh_kv;
+    int            page_size;     /* power of two */
+    int            batch;
+    int            nh_q;
+    const void*    q;             /* bf16 device, row b at q + b * q_stride, [nh_q, 128] */
+    int64_t        q_stride;
+    void*          out;           /* bf16 device, row b at out + b * out_stride */
+    int64_t        out_stride;
+    const int32_t* seq_lens;      /* [batch] int32 device: tokens attended, all in the pool */
+    const int32_t* page_table;    /* [batch, pt_stride] int32 device */
+    int            pt_stride;
+    float          softmax_scale;
+    float*         lse_out;       /* [batch, nh_q] or NULL */
+    int            sync_and_check;/* non-zero: wait for the stream and report a device-side failure */
+    char*          err_buf;       /* optional buffer for the error text */
+    int            err_buf_len;
+} dkv_noalloc_args;
+
+int dkv_decode_noalloc(const dkv_noalloc_args* args, void* stream);
+
 /* Host-link helper: device-side copy kernel reading `bytes` from src (host-mapped or device)
  * into dst (device) with plain vector loads; used to measure the zero-copy roofline. */
 int dkv_stream_copy(dkv_context* ctx, void* dst, const void* src, int64_t bytes, void* stream);
