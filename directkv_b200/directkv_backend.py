@@ -1,0 +1,378 @@
+"""SGLang attention backend over the B200 engine.
+
+Same class name, constructor and method surface as the reference's ``DirectKVBackend``
+(directkv/directkv_backend.py:63-928): ``init_forward_metadata``, ``forward_decode``,
+``forward_extend`` and the four CUDA-graph hooks, reading the same fields of ``ForwardBatch``,
+``RadixAttention`` and ``ModelRunner`` (:68-76, :159-196).
+
+What is different underneath
+  * One engine call per layer and step for the WHOLE ragged batch: no bucketing by 64-aligned
+    length, no zero-padded 64-row tiles, no per-request SDPA fallback (the kernels take any
+    length and any ``NH_q % NH_kv == 0``).
+  * The request pool is read and written in place through a row map (the reference gathers a
+    pageable copy per bucket, directkv/directkv_request_pool.py:148-152, so its kernel's write-back
+    never reaches the pool).
+  * Under CUDA graphs every request keeps its own length: lengths and rows live in device tensors
+    that the replay hook refreshes (the reference forces one common padded length,
+    directkv/directkv_backend.py:483-494).
+  * When the layer's hidden states were not captured (no hook fired) the step runs over SGLang's
+    token pool with the K/V SGLang computed - the data flow of the reference's
+    ``_sdpa_decode_manual`` / ``_sdpa_extend_manual`` (:835-891) - still on the engine.
+"""
+
+from __future__ import annotations
+
+import logging
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from . import kernel
+from ._lib import get_context
+from .directkv_request_pool import DirectKVRequestPool
+from .sglang_compat import AttentionBackend, get_attention_tp_size
+
+logger = logging.getLogger(__name__)
+
+_TILE = 64                       # directkv/directkv_backend.py:42
+_TOKEN_POOL_LAYER_BASE = 1 << 20  # engine layer ids of the token-pool registrations
+
+
+def _pad64(n: int) -> int:
+    return -(-int(n) // _TILE) * _TILE
+
+
+@dataclass
+class _FwdMeta:
+    """Host copies made once per step (directkv/directkv_backend.py:52-57) plus their device twins."""
+    seq_lens_cpu: List[int]
+    req_pool_indices_cpu: List[int]
+    extend_seq_lens_cpu: Optional[List[int]]
+    extend_prefix_lens_cpu: Optional[List[int]]
+    seq_lens_dev: Optional[torch.Tensor] = None       # int32 [bs]
+    rows_dev: Optional[torch.Tensor] = None           # int32 [bs] request-pool rows
+    req_idx_dev: Optional[torch.Tensor] = None        # int32 [bs] rows of req_to_token
+
+
+class DirectKVBackend(AttentionBackend):
+    _NAME = "directkv"
+    _TAG = "[DirectKV]"
+
+    def __init__(self, model_runner):
+        super().__init__()
+        tp = get_attention_tp_size()
+        cfg = model_runner.model_config
+        self.num_q_heads = cfg.num_attention_heads // tp
+        self.num_kv_heads = cfg.get_num_kv_heads(tp)
+        self.head_dim = cfg.head_dim
+        self.v_head_dim = getattr(cfg, "v_head_dim", None) or cfg.head_dim
+        self.hidden_size = cfg.hidden_size
+        self.device = model_runner.device
+        self._check_args(model_runner)
+
+        # The engine handles every grouping with NH_q % NH_kv == 0; anything else has no meaning for
+        # grouped attention (the reference logs and falls back to a path that needs the same property).
+        self._use_kernel = (self.num_q_heads % self.num_kv_heads == 0)
+        if not self._use_kernel:
+            raise ValueError(f"{self._NAME}: NH_q={self.num_q_heads} is not a multiple of NH_kv={self.num_kv_heads}")
+
+        # The three entry points the reference binds in its constructor (:80-96)
+        self._directkv_fwd = kernel.smpv2_fwd
+        self._directkv_init_tma = kernel.smpv2_init_tma
+        self._directkv_fwd_graph = kernel.smpv2_fwd_graph
+
+        self._wk: Dict[int, torch.Tensor] = {}
+        self._wv: Dict[int, torch.Tensor] = {}
+        self._cos_sin: Optional[torch.Tensor] = None
+        self._hidden: Dict[int, torch.Tensor] = {}
+        self._hooks_ready = False
+        self._model_runner = model_runner
+        self._fwd_meta: Optional[_FwdMeta] = None
+        self._pool_cls = DirectKVRequestPool
+        self._pool: Optional[DirectKVRequestPool] = None
+        self._registered: set = set()
+        self._token_registered: Dict[int, int] = {}
+        self._active_req_ids: set = set()
+        self._last_seen: Dict[int, int] = {}
+        self._step_no = 0
+        self._start_layer = 0
+        # CUDA-graph state: device tensors with stable addresses, refreshed before each replay
+        self._cg_max_bs = 0
+        self._cg_seq_lens: Optional[torch.Tensor] = None
+        self._cg_rows: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ checks
+    def _check_args(self, runner) -> None:
+        """Same three conditions as directkv/directkv_backend.py:159-169."""
+        if not runner.server_args.disable_radix_cache:
+            raise ValueError(f"{self._NAME} requires --disable-radix-cache")
+        if self.head_dim != 128:
+            raise ValueError(f"{self._NAME} requires head_dim=128, got {self.head_dim}. "
+                             "Use a compatible model (e.g. OPT-6.7B, Llama-3-8B with GQA mod).")
+        if runner.model_config.dtype not in (torch.bfloat16,):
+            raise ValueError(f"{self._NAME} requires bfloat16 model weights.")
+
+    # ------------------------------------------------------------------ pool
+    def _ensure_pool(self) -> None:
+        """Pool sizing of directkv/directkv_backend.py:174-197; layers are registered with the engine here."""
+        if self._pool is None:
+            mr = self._model_runner
+            max_reqs = min(mr.req_to_token_pool.size, 64)
+            context_len = getattr(mr.model_config, "context_len", 2048)
+            max_seqlen = min(mr.req_to_token_pool.req_to_token.shape[1], context_len)
+            self._start_layer = getattr(mr, "start_layer", 0)
+            self._pool = self._pool_cls(
+                max_reqs=max_reqs, max_seqlen=max_seqlen, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
+                num_layers=mr.model_config.num_hidden_layers, start_layer=self._start_layer,
+            )
+            logger.info(f"{self._TAG} Pool: {self._pool}")
+        for lid in self._wk:
+            if lid not in self._registered:
+                k_rows, v_rows = self._pool.get_row_tensor(lid)
+                kernel.register_layer(lid, k_rows, v_rows, self._wk[lid], self._wv[lid], self._cos_sin, page_size=1,
+                                      row_stride=self._pool.max_seqlen_pad, device=self._device_index())
+                self._registered.add(lid)
+
+    def _device_index(self) -> Optional[int]:
+        d = torch.device(self.device)
+        return d.index if d.index is not None else (torch.cuda.current_device() if torch.cuda.is_available() else None)
+
+    # ------------------------------------------------------------------ hooks / weights
+    def _setup_hooks(self) -> None:
+        """Walks the model like directkv/directkv_backend.py:202-234: every module with an ``attn`` child that
+        has a ``layer_id`` gives its K/V projection weights and gets a pre-hook that records its input."""
+        model = self._model_runner.model
+        self._start_layer = getattr(self._model_runner, "start_layer", 0)
+        n = 0
+        for _name, module in model.named_modules():
+            layer_id = getattr(getattr(module, "attn", None), "layer_id", None)
+            if layer_id is None:
+                continue
+            wk, wv = self._extract_weights(module, layer_id)
+            if wk is None:
+                continue
+            self._wk[layer_id], self._wv[layer_id] = wk, wv
+            if self._cos_sin is None:
+                self._cos_sin = self._extract_cos_sin(module)
+            module.register_forward_pre_hook(
+                lambda _m, args, kwargs, _lid=layer_id: self._capture_hs(_lid, args, kwargs), with_kwargs=True)
+            n += 1
+        logger.info(f"{self._TAG} Hooked {n} layers; RoPE={'yes' if self._cos_sin is not None else 'no (OPT)'}.")
+        self._hooks_ready = True
+
+    def _capture_hs(self, layer_id: int, args, kwargs=None) -> None:
+        if kwargs and "hidden_states" in kwargs:
+            self._hidden[layer_id] = kwargs["hidden_states"]
+        elif args:
+            self._hidden[layer_id] = args[0]
+
+    def _extract_weights(self, module, layer_id: int) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+        """K and V projection weights as [NH_kv, D, H] (directkv/directkv_backend.py:243-271).  As in the
+        reference only ``.weight`` is used: a model with biased k/v projections (OPT) loses the bias."""
+        nh_kv, nh_q, d, h = self.num_kv_heads, self.num_q_heads, self.head_dim, self.hidden_size
+        qkv = getattr(module, "qkv_proj", None)
+        if qkv is not None and hasattr(qkv, "weight"):
+            w = qkv.weight.detach()
+            k0 = nh_q * d
+            k1 = k0 + nh_kv * d
+            return (w[k0:k1].contiguous().view(nh_kv, d, h), w[k1:k1 + nh_kv * d].contiguous().view(nh_kv, d, h))
+        kp, vp = getattr(module, "k_proj", None), getattr(module, "v_proj", None)
+        if kp is not None and vp is not None and hasattr(kp, "weight") and hasattr(vp, "weight"):
+            return (kp.weight.detach().contiguous().view(nh_kv, d, h), vp.weight.detach().contiguous().view(nh_kv, d, h))
+        logger.warning(f"{self._TAG} Layer {layer_id}: cannot extract weights.")
+        return None, None
+
+    def _extract_cos_sin(self, module) -> Optional[torch.Tensor]:
+        """[max_pos, D] fp32 table = [cos | sin] from whatever the rotary module offers
+        (directkv/directkv_backend.py:273-305); None when the model has no rotary embedding."""
+        rotary = getattr(module, "rotary_emb", None)
+        if rotary is None:
+            return None
+        d = self.head_dim
+        fused = getattr(rotary, "cos_sin_cache", None)
+        if fused is not None and fused.shape[-1] == d:
+            return fused.float().to(self.device).contiguous()
+        for cname, sname in (("cos_cached", "sin_cached"), ("_cos_cached", "_sin_cached"), ("cos", "sin")):
+            cos, sin = getattr(rotary, cname, None), getattr(rotary, sname, None)
+            if cos is None or sin is None:
+                continue
+            while cos.dim() > 2:
+                cos, sin = cos.squeeze(0), sin.squeeze(0)
+            if cos.dim() == 2 and cos.shape[-1] in (d // 2, d):
+                half = d // 2
+                return torch.cat([cos[:, :half], sin[:, :half]], dim=-1).float().to(self.device).contiguous()
+        inv_freq = getattr(rotary, "inv_freq", None)
+        if inv_freq is not None:
+            max_pos = getattr(rotary, "max_position_embeddings", 8192)
+            t = torch.arange(max_pos, dtype=torch.float32, device=self.device)
+            fq = torch.outer(t, inv_freq.float().to(self.device))
+            return torch.cat([fq.cos(), fq.sin()], dim=-1).contiguous()
+        return None
+
+    # ------------------------------------------------------------------ per-step metadata
+    def _sync_rows(self, req_ids: List[int], free_absent: bool = True) -> None:
+        """Row lifecycle.  In a DECODE batch every running request is present, so a request that is
+        absent has finished: its row is freed first, then new requests get rows - the reference's policy
+        (directkv/directkv_backend.py:323-335).  An EXTEND batch carries only the requests being
+        prefilled, so absence means nothing there (the reference frees - and later zero-fills - the rows
+        of running requests in that case); rows are then only reclaimed, oldest first, when the pool
+        is full."""
+        current = set(req_ids)
+        self._step_no += 1
+        if free_absent:
+            for rid in self._active_req_ids - current:
+                self._pool.free(rid)
+                self._last_seen.pop(rid, None)
+            self._active_req_ids &= current
+        for rid in req_ids:
+            if rid not in self._active_req_ids:
+                if not self._pool._free:
+                    idle = sorted((r for r in self._active_req_ids if r not in current), key=lambda r: self._last_seen.get(r, 0))
+                    if idle:
+                        self._pool.free(idle[0])
+                        self._active_req_ids.discard(idle[0])
+                        self._last_seen.pop(idle[0], None)
+                self._pool.alloc(rid)
+                self._active_req_ids.add(rid)
+            self._last_seen[rid] = self._step_no
+
+    def init_forward_metadata(self, forward_batch) -> None:
+        if forward_batch.forward_mode.is_idle():
+            self._fwd_meta = None
+            return
+        if not self._hooks_ready:
+            self._setup_hooks()
+        seq_lens_cpu = forward_batch.seq_lens.cpu().tolist()
+        req_ids_cpu = forward_batch.req_pool_indices.cpu().tolist()
+        self._ensure_pool()
+        self._sync_rows(req_ids_cpu, free_absent=forward_batch.forward_mode.is_decode())
+        self._fwd_meta = _FwdMeta(
+            seq_lens_cpu=seq_lens_cpu,
+            req_pool_indices_cpu=req_ids_cpu,
+            extend_seq_lens_cpu=getattr(forward_batch, "extend_seq_lens_cpu", None),
+            extend_prefix_lens_cpu=getattr(forward_batch, "extend_prefix_lens_cpu", None),
+            seq_lens_dev=forward_batch.seq_lens.to(device=self.device, dtype=torch.int32),
+            rows_dev=self._pool.row_table(req_ids_cpu, self.device),
+            req_idx_dev=forward_batch.req_pool_indices.to(device=self.device, dtype=torch.int32),
+        )
+
+    # ------------------------------------------------------------------ CUDA graphs
+    def init_cuda_graph_state(self, max_bs: int, max_num_tokens: int) -> None:
+        if not self._hooks_ready:
+            self._setup_hooks()
+        self._ensure_pool()
+        self._cg_max_bs = max_bs
+        self._cg_seq_lens = torch.ones(max_bs, dtype=torch.int32, device=self.device)
+        self._cg_rows = torch.zeros(max_bs, dtype=torch.int32, device=self.device)
+        # Scratch for max_bs requests is sized now: nothing is allocated while a graph is captured.
+        get_context(self._device_index()).reserve(max_bs, self.num_q_heads, self.num_kv_heads, self.hidden_size)
+        logger.info(f"{self._TAG} CUDA graph state: max_bs={max_bs}, layers={len(self._wk)}.")
+
+    def _graph_meta(self, bs: int, req_pool_indices, seq_lens_cpu: List[int]) -> None:
+        rid_list = req_pool_indices[:bs].cpu().tolist()
+        self._ensure_pool()
+        self._sync_rows(rid_list)
+        self._cg_rows[:bs].copy_(self._pool.row_table(rid_list), non_blocking=True)
+        self._fwd_meta = _FwdMeta(
+            seq_lens_cpu=seq_lens_cpu, req_pool_indices_cpu=rid_list, extend_seq_lens_cpu=None,
+            extend_prefix_lens_cpu=None, seq_lens_dev=self._cg_seq_lens[:bs], rows_dev=self._cg_rows[:bs],
+            req_idx_dev=req_pool_indices[:bs].to(torch.int32),
+        )
+
+    def init_forward_metadata_capture_cuda_graph(self, bs, num_tokens, req_pool_indices, seq_lens, encoder_lens,
+                                                 forward_mode, spec_info) -> None:
+        fill = self.get_cuda_graph_seq_len_fill_value()
+        self._cg_seq_lens[:bs].fill_(fill)
+        self._graph_meta(bs, req_pool_indices, [fill] * bs)
+
+    def init_forward_metadata_replay_cuda_graph(self, bs, req_pool_indices, seq_lens, seq_lens_sum, encoder_lens,
+                                                forward_mode, spec_info, seq_lens_cpu=None) -> None:
+        sl_cpu = seq_lens_cpu.tolist() if seq_lens_cpu is not None else seq_lens[:bs].cpu().tolist()
+        self._cg_seq_lens[:bs].copy_(seq_lens[:bs])          # every request keeps its OWN length
+        self._graph_meta(bs, req_pool_indices, sl_cpu)
+
+    def get_cuda_graph_seq_len_fill_value(self) -> int:
+        return _TILE
+
+    # ------------------------------------------------------------------ decode
+    def forward_decode(self, q, k, v, layer, forward_batch, save_kv_cache: bool = True) -> torch.Tensor:
+        lid, meta = layer.layer_id, self._fwd_meta
+        bs = forward_batch.batch_size
+        if meta is None:
+            return torch.zeros(bs, self.num_q_heads * self.head_dim, dtype=q.dtype, device=self.device)
+        x = self._hidden.pop(lid, None)
+        q2 = q.reshape(bs, self.num_q_heads * self.head_dim).contiguous()
+        if x is None or lid not in self._registered:
+            return self._decode_token_pool(q2, k, v, layer, forward_batch)
+        return kernel.decode(
+            lid, q2, meta.seq_lens_dev[:bs], float(layer.scaling), row_map=meta.rows_dev[:bs],
+            x=x.reshape(bs, self.hidden_size).contiguous(), save_kv_cache=save_kv_cache,
+        )
+
+    def _token_layer(self, layer, forward_batch) -> int:
+        """Engine registration of SGLang's token-indexed pool for this layer (page size 1 = per-token slots)."""
+        lid = layer.layer_id
+        pool = forward_batch.token_to_kv_pool
+        k_buf, v_buf = pool.get_key_buffer(lid), pool.get_value_buffer(lid)
+        eng = _TOKEN_POOL_LAYER_BASE + lid
+        if self._token_registered.get(lid) != k_buf.data_ptr():
+            kernel.register_layer(eng, k_buf, v_buf, page_size=1, device=self._device_index())
+            self._token_registered[lid] = k_buf.data_ptr()
+        return eng
+
+    def _decode_token_pool(self, q2, k, v, layer, forward_batch) -> torch.Tensor:
+        """Data flow of ``_sdpa_decode_manual`` (:835-859): store k, v at ``out_cache_loc``, attend the slots
+        ``req_to_token[req, :seq_len]``."""
+        meta = self._fwd_meta
+        bs = forward_batch.batch_size
+        forward_batch.token_to_kv_pool.set_kv_buffer(layer, forward_batch.out_cache_loc, k, v)
+        eng = self._token_layer(layer, forward_batch)
+        table = forward_batch.req_to_token_pool.req_to_token
+        return kernel.decode(eng, q2, meta.seq_lens_dev[:bs], float(layer.scaling), page_table=table,
+                             row_map=meta.req_idx_dev[:bs])
+
+    # ------------------------------------------------------------------ extend
+    def forward_extend(self, q, k, v, layer, forward_batch, save_kv_cache: bool = True) -> torch.Tensor:
+        lid, meta = layer.layer_id, self._fwd_meta
+        bs = forward_batch.batch_size
+        nh_q, d = self.num_q_heads, self.head_dim
+        if meta is None:
+            return q.new_zeros(q.shape[0], nh_q * d)
+        x_all = self._hidden.pop(lid, None)
+        ext, pre = meta.extend_seq_lens_cpu, meta.extend_prefix_lens_cpu
+        if x_all is None or lid not in self._registered or ext is None:
+            return self._extend_token_pool(q, k, v, layer, forward_batch)
+        out = torch.empty(q.shape[0], nh_q * d, dtype=q.dtype, device=q.device)
+        off = 0
+        for i in range(bs):
+            n_new = int(ext[i])
+            n_pre = int(pre[i]) if pre else 0
+            if n_new == 0:
+                continue
+            x_i = x_all[off:off + n_new].reshape(1, n_new, self.hidden_size).contiguous()
+            q_i = q[off:off + n_new].reshape(1, n_new, nh_q, d).contiguous()
+            o_i = kernel.extend(lid, x_i, q_i, float(layer.scaling), True, n_pre, -1, row_map=meta.rows_dev[i:i + 1])
+            out[off:off + n_new] = o_i.view(n_new, nh_q * d)
+            off += n_new
+        return out
+
+    def _extend_token_pool(self, q, k, v, layer, forward_batch) -> torch.Tensor:
+        """Data flow of ``_sdpa_extend_manual`` (:861-891) on the engine: store k, v, then every new row
+        attends slots ``req_to_token[req, :prefix + i + 1]`` (the triu(diagonal=prefix+1) mask)."""
+        meta = self._fwd_meta
+        bs = forward_batch.batch_size
+        nh_q, d = self.num_q_heads, self.head_dim
+        forward_batch.token_to_kv_pool.set_kv_buffer(layer, forward_batch.out_cache_loc, k, v)
+        eng = self._token_layer(layer, forward_batch)
+        ext = meta.extend_seq_lens_cpu or [meta.seq_lens_cpu[i] for i in range(bs)]
+        pre = meta.extend_prefix_lens_cpu or [0] * bs
+        vlen, vrow = [], []
+        for i in range(bs):
+            vlen += [int(pre[i]) + j + 1 for j in range(int(ext[i]))]
+            vrow += [meta.req_pool_indices_cpu[i]] * int(ext[i])
+        vlen_t = torch.tensor(vlen, dtype=torch.int32).to(self.device, non_blocking=True)
+        vrow_t = torch.tensor(vrow, dtype=torch.int32).to(self.device, non_blocking=True)
+        q2 = q.reshape(-1, nh_q * d).contiguous()
+        return kernel.decode(eng, q2, vlen_t, float(layer.scaling),
+                             page_table=forward_batch.req_to_token_pool.req_to_token, row_map=vrow_t)
