@@ -73,6 +73,7 @@ class DecodeArgs(C.Structure):
         ("softmax_scale", C.c_float),
         ("lse_out", C.c_void_p),
         ("partial_out", C.c_void_p),
+        ("pos_offset", C.c_void_p),
     ]
 
 

@@ -63,6 +63,7 @@ struct PrepParams {
     int* tok_slot;            // [batch] slot the token is stored to, or -1
     const int* page_table;
     const int* row_map;
+    const int* pos_offset;    // [batch] added to the RoPE position, or nullptr
     int pt_stride, page_size, page_shift;
     long long row_stride;
     int save;
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams pp) {
                     else
                         slot = static_cast<long long>(row) * pp.row_stride + pos;
                 }
-                pp.tok_pos[b] = pos;
+                pp.tok_pos[b] = pos + (pp.pos_offset ? pp.pos_offset[b] : 0);
                 pp.tok_slot[b] = static_cast<int>(slot);
             }
         }

@@ -638,6 +638,7 @@ int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) {
     prep.tok_slot = tok_slot;
     prep.page_table = a->page_table;
     prep.row_map = a->row_map;
+    prep.pos_offset = a->pos_offset;
     prep.pt_stride = a->pt_stride;
     prep.page_size = L.d.page_size;
     prep.page_shift = L.page_shift;

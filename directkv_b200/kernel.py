@@ -122,6 +122,7 @@ def decode(
     lse_out: Optional[torch.Tensor] = None,
     partial_out: Optional[torch.Tensor] = None,  # [B, NH_q, 132] fp32: unnormalised (O, m, l)
     normalized: bool = True,
+    pos_offset: Optional[torch.Tensor] = None,   # [B] int32 CUDA: added to seq_len-1 for the RoPE position
 ) -> Optional[torch.Tensor]:
     """One decode step of one registered layer for a ragged batch.  Returns O with q's shape."""
     _check_cuda_bf16(q, "q")
@@ -152,6 +153,8 @@ def decode(
     if partial_out is not None:
         _chk(partial_out.is_cuda and partial_out.dtype == torch.float32 and partial_out.is_contiguous()
              and partial_out.numel() == b * nh_q * PARTIAL_STRIDE, "partial_out must be [B, NH_q, 132] fp32 CUDA")
+    if pos_offset is not None:
+        _chk(pos_offset.is_cuda and pos_offset.dtype == torch.int32 and pos_offset.numel() == b, "pos_offset must be [B] int32 CUDA")
     if b == 0:
         return out
     a = DecodeArgs(
@@ -160,7 +163,7 @@ def decode(
         page_table=_ptr(page_table), pt_stride=0 if page_table is None else page_table.stride(0),
         row_map=_ptr(row_map), new_mode=mode, x=_ptr(x), k_new=_ptr(k_new), v_new=_ptr(v_new),
         save_kv_cache=1 if save_kv_cache else 0, softmax_scale=float(softmax_scale),
-        lse_out=_ptr(lse_out), partial_out=_ptr(partial_out),
+        lse_out=_ptr(lse_out), partial_out=_ptr(partial_out), pos_offset=_ptr(pos_offset),
     )
     ctx = get_context(q.device.index)
     _lib.check(_lib.load().dkv_decode(ctx.handle, C.byref(a), _stream()))

@@ -137,6 +137,8 @@ typedef struct {
     float          softmax_scale;
     float*         lse_out;      /* [batch, nh_q] natural-log LSE, or NULL */
     float*         partial_out;  /* [batch, nh_q, 132] unnormalised (O[128], m_log2, l, pad) or NULL */
+    const int32_t* pos_offset;   /* [batch] or NULL: added to seq_lens[b] - 1 to get the new token's absolute
+                                    (RoPE) position when this pool holds only a later part of the sequence */
 } dkv_decode_args;
 
 int dkv_decode(dkv_context* ctx, const dkv_decode_args* args, void* stream);
