@@ -162,8 +162,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--variant", type=int, default=None, help="override the streaming-kernel variant")
-    ap.add_argument("--only", default="all", choices=["all", "hbm"],
-                    help="hbm: time only the HBM-resident mode (short run for profiler captures)")
+    ap.add_argument("--only", default="all", choices=["all", "hbm", "host"],
+                    help="hbm / host: time only that mode (short runs for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -255,6 +255,17 @@ def main():
     if rank == 0:
         sampler.start()
 
+    if args.only == "host":
+        ms = timed(step_e2e, max(1, min(args.steps, 20)), args.warmup)
+        ctx.raise_on_status()
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"metric": METRIC, "value": kv_all_ranks / ms / 1e6, "unit": UNIT, "ms_per_step": ms,
+                              "partial": "host-KV mode only"}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # ---- HBM-resident mode: `value` and the roofline of the streaming kernel -------------------------
     for _ in range(args.warmup):
         step_hbm()
@@ -335,9 +346,9 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) per launch of the streaming kernel from the ncu capture summarised in
-# profiles/; None until a capture of this workload exists.
-TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes (read 980.18 MB + write 5.03 MB) per launch of the streaming kernel on this workload, from the
+# ncu capture summarised in profiles/attn_partial_kernel_c2_hbm.md.
+TRAFFIC_BYTES_PER_LAUNCH = 985_208_320
 
 if __name__ == "__main__":
     main()
