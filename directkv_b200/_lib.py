@@ -115,6 +115,11 @@ SIGNATURES = {
     "dkv_layer_register": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(LayerDesc)]),
     "dkv_layer_unregister": (C.c_int, [C.c_void_p, C.c_int]),
     "dkv_decode": (C.c_int, [C.c_void_p, C.POINTER(DecodeArgs), C.c_void_p]),
+    "dkv_exchange_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.POINTER(C.c_void_p)]),
+    "dkv_exchange_handle": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "dkv_exchange_connect": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p]),
+    "dkv_exchange_destroy": (C.c_int, [C.c_void_p]),
+    "dkv_decode_exchange": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(DecodeArgs), C.c_void_p, C.c_void_p, C.c_void_p]),
     "dkv_merge_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
     "dkv_smpv2_fwd": (C.c_int, [C.c_void_p] + [C.c_void_p] * 6 + [C.c_void_p, C.c_int] + [C.c_int] * 6
                       + [C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),

@@ -26,6 +26,7 @@ constexpr int kRowBytes      = kHeadDim * 2;                    // one token, on
 constexpr int kTileBytes     = kTileTokens * kRowBytes;         // 4096: K or V of one tile
 constexpr int kStageBytes    = 2 * kTileBytes;                  // K + V
 constexpr int kPartialStride = 132;                             // 128 O + m + l + 2 pad (fp32)
+constexpr int kMaxExchangeRanks = 8;                            // GPUs of one box
 
 struct AttnParams {
     const __nv_bfloat16* q;        // query rows; row b starts at q + b * q_stride, then [NH_q, 128]
@@ -411,6 +412,14 @@ struct MergeParams {
     long long out_stride;
     float* lse;                      // [B, NH_q] natural-log LSE, or nullptr
     float* part_out;                 // [B, NH_q, kPartialStride] unnormalised partial, or nullptr
+    // Sequence split without a collective call: the unnormalised record of every row is stored into the
+    // exchange buffer of EVERY rank (plain stores over NVLink for peers) at [x_rank][row], then one
+    // system-scope increment per row tells that rank how many rows of x_rank have landed.
+    int x_world;                     // 0: off
+    int x_rank;
+    long long x_max_rows;
+    float* x_part[kMaxExchangeRanks];            // rank p's buffer [x_world, x_max_rows, kPartialStride]
+    unsigned int* x_count[kMaxExchangeRanks];    // rank p's arrival counters [x_world]
 };
 
 __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams mp) {
@@ -480,6 +489,17 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams mp) {
             po[129] = l;
         }
     }
+    if (mp.x_world > 0) {
+        const long long row = static_cast<long long>(b) * p.nh_q + hq;
+        for (int r = 0; r < mp.x_world; ++r) {
+            float* po = mp.x_part[r] + (static_cast<long long>(mp.x_rank) * mp.x_max_rows + row) * kPartialStride;
+            *reinterpret_cast<float4*>(po + 4 * lane) = acc;
+            if (lane == 0) *reinterpret_cast<float2*>(po + 128) = make_float2(m, l);
+        }
+        __threadfence_system();      // the record is visible system-wide before the count moves
+        __syncwarp();
+        if (lane < mp.x_world) atomicAdd_system(mp.x_count[lane] + mp.x_rank, 1u);
+    }
     if (mp.out != nullptr) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
         uint2 w;
@@ -524,6 +544,76 @@ __global__ void __launch_bounds__(128) merge_rank_partials_kernel(const float* _
     w.y = pack_bf16x2(acc.z * inv, acc.w * inv);
     *reinterpret_cast<uint2*>(out + r * kHeadDim + 4 * lane) = w;
     if (lse != nullptr && lane == 0) lse[r] = (l > 0.f) ? m * 0.6931471805599453f + logf(l) : -INFINITY;
+}
+
+// ---------------------------------------------------------------------------
+// Consumer side of the exchange: one warp per row waits (bounded) until every rank's count says
+// its records for this step have landed in THIS GPU's buffer, then merges them from local memory.
+// ---------------------------------------------------------------------------
+struct ExchangeMergeParams {
+    const float* parts;                       // this rank's buffer [world, max_rows, kPartialStride]
+    const unsigned int* count;                // this rank's arrival counters [world]
+    unsigned int expected[kMaxExchangeRanks]; // cumulative rows each rank must have delivered
+    int world;
+    long long max_rows, rows;
+    __nv_bfloat16* out;                       // [rows, 128]
+    float* lse;                               // [rows] or nullptr
+    unsigned int* status;
+};
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__global__ void __launch_bounds__(128) merge_exchange_kernel(const ExchangeMergeParams ep) {
+    const int lane = threadIdx.x & 31;
+    const long long r = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= ep.rows) return;
+    // lane k watches rank k's counter
+    bool ok = true;
+    if (lane < ep.world) {
+        // wrap-safe comparison: the counters only grow
+        if (static_cast<int>(ld_acquire_sys(ep.count + lane) - ep.expected[lane]) < 0) {
+            const unsigned long long t0 = globaltimer_ns();
+            for (;;) {
+                if (static_cast<int>(ld_acquire_sys(ep.count + lane) - ep.expected[lane]) >= 0) break;
+                if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                    ok = false;
+                    break;
+                }
+                __nanosleep(200);
+            }
+        }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) {
+        if (lane == 0) atomicOr(ep.status, kStatusWaitTimeout);
+        return;
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float m = -INFINITY, l = 0.f;
+    for (int k = 0; k < ep.world; ++k) {
+        const float* rec = ep.parts + (static_cast<long long>(k) * ep.max_rows + r) * kPartialStride;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(rec + 128));
+        const float4 oi = __ldcg(reinterpret_cast<const float4*>(rec + 4 * lane));
+        const float mn = fmaxf(m, ml.x);
+        const float mu = (mn == -INFINITY) ? 0.f : mn;
+        const float a = exp2f(m - mu), c = exp2f(ml.x - mu);
+        acc.x = acc.x * a + oi.x * c;
+        acc.y = acc.y * a + oi.y * c;
+        acc.z = acc.z * a + oi.z * c;
+        acc.w = acc.w * a + oi.w * c;
+        l = l * a + ml.y * c;
+        m = mn;
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    uint2 w;
+    w.x = pack_bf16x2(acc.x * inv, acc.y * inv);
+    w.y = pack_bf16x2(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(ep.out + r * kHeadDim + 4 * lane) = w;
+    if (ep.lse != nullptr && lane == 0) ep.lse[r] = (l > 0.f) ? m * 0.6931471805599453f + logf(l) : -INFINITY;
 }
 
 }  // namespace dkv

@@ -125,6 +125,19 @@ struct dkv_context {
     size_t attn_events_used = 0;
 };
 
+// Peer-memory exchange of sequence-split partials (one per process group of <= 8 GPUs of a box).
+struct dkv_exchange {
+    dkv_context* ctx = nullptr;
+    int rank = 0, world = 0;
+    long long max_rows = 0;
+    uint8_t* local = nullptr;                       // cudaMalloc: records [world, max_rows, 132] fp32, then counters
+    size_t part_bytes = 0;
+    float* part[dkv::kMaxExchangeRanks] = {nullptr};         // every rank's record area, as mapped into this process
+    unsigned int* count[dkv::kMaxExchangeRanks] = {nullptr}; // every rank's arrival counters
+    void* opened[dkv::kMaxExchangeRanks] = {nullptr};        // IPC mappings to close
+    unsigned int expected[dkv::kMaxExchangeRanks] = {0};     // rows each rank has delivered so far (cumulative)
+};
+
 namespace {
 
 // ---------------------------------------------------------------------------
@@ -587,7 +600,7 @@ int dkv_layer_unregister(dkv_context* ctx, int layer_id) {
     return DKV_OK;
 }
 
-int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) {
+static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream, dkv_exchange* ex) {
     DKV_REQUIRE(ctx != nullptr && a != nullptr, "ctx / args is NULL");
     auto it = ctx->layers.find(a->layer_id);
     if (it == ctx->layers.end())
@@ -599,7 +612,7 @@ int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) {
     DKV_REQUIRE(a->batch > 0, "batch must be >= 0");
     DKV_REQUIRE(a->nh_q > 0 && a->nh_q % nh_kv == 0, "nh_q (%d) must be a multiple of nh_kv (%d)", a->nh_q, nh_kv);
     DKV_REQUIRE(a->q != nullptr && a->seq_lens != nullptr, "q / seq_lens must not be NULL");
-    DKV_REQUIRE(a->out != nullptr || a->partial_out != nullptr, "out or partial_out must be given");
+    DKV_REQUIRE(a->out != nullptr || a->partial_out != nullptr || ex != nullptr, "out or partial_out must be given");
     DKV_REQUIRE(a->q_stride >= static_cast<int64_t>(a->nh_q) * 128 && a->q_stride % 8 == 0, "q_stride too small or unaligned");
     DKV_REQUIRE((reinterpret_cast<uintptr_t>(a->q) & 15) == 0, "q must be 16-byte aligned");
     if (a->out) {
@@ -691,7 +704,111 @@ int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) {
     mp.out_stride = a->out_stride;
     mp.lse = a->lse_out;
     mp.part_out = a->partial_out;
+    if (ex != nullptr) {
+        mp.x_world = ex->world;
+        mp.x_rank = ex->rank;
+        mp.x_max_rows = ex->max_rows;
+        for (int r = 0; r < ex->world; ++r) {
+            mp.x_part[r] = ex->part[r];
+            mp.x_count[r] = ex->count[r];
+        }
+    }
     return launch_attention(ctx, L, ap, paged, mp, st, a->new_mode == DKV_NEW_PROJECT ? ctx->ev_join : nullptr);
+}
+
+int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) { return decode_impl(ctx, a, stream, nullptr); }
+
+int dkv_exchange_create(dkv_context* ctx, int rank, int world, int64_t max_rows, dkv_exchange** out) {
+    DKV_REQUIRE(ctx != nullptr && out != nullptr, "ctx / out is NULL");
+    DKV_REQUIRE(world >= 1 && world <= kMaxExchangeRanks && rank >= 0 && rank < world, "bad rank %d / world %d (at most %d ranks)",
+                rank, world, kMaxExchangeRanks);
+    DKV_REQUIRE(max_rows > 0, "max_rows must be positive");
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    dkv_exchange* ex = new dkv_exchange();
+    ex->ctx = ctx;
+    ex->rank = rank;
+    ex->world = world;
+    ex->max_rows = max_rows;
+    ex->part_bytes = align256(static_cast<size_t>(world) * max_rows * kPartialStride * sizeof(float));
+    cudaError_t e = cudaMalloc(&ex->local, ex->part_bytes + 256);
+    if (e == cudaSuccess) e = cudaMemset(ex->local, 0, ex->part_bytes + 256);
+    if (e != cudaSuccess) {
+        delete ex;
+        return fail(DKV_ERR_CUDA, "exchange buffer allocation failed: %s", cudaGetErrorString(e));
+    }
+    ex->part[rank] = reinterpret_cast<float*>(ex->local);
+    ex->count[rank] = reinterpret_cast<unsigned int*>(ex->local + ex->part_bytes);
+    *out = ex;
+    return DKV_OK;
+}
+
+int dkv_exchange_handle(dkv_exchange* ex, void* handle_out_64_bytes) {
+    DKV_REQUIRE(ex != nullptr && handle_out_64_bytes != nullptr, "NULL argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    DKV_CUDA(cudaSetDevice(ex->ctx->device));
+    cudaIpcMemHandle_t h;
+    DKV_CUDA(cudaIpcGetMemHandle(&h, ex->local));
+    memcpy(handle_out_64_bytes, &h, sizeof(h));
+    return DKV_OK;
+}
+
+int dkv_exchange_connect(dkv_exchange* ex, int peer_rank, const void* handle_64_bytes) {
+    DKV_REQUIRE(ex != nullptr && handle_64_bytes != nullptr, "NULL argument");
+    DKV_REQUIRE(peer_rank >= 0 && peer_rank < ex->world && peer_rank != ex->rank, "bad peer rank %d", peer_rank);
+    DKV_CUDA(cudaSetDevice(ex->ctx->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle_64_bytes, sizeof(h));
+    void* base = nullptr;
+    DKV_CUDA(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+    ex->opened[peer_rank] = base;
+    ex->part[peer_rank] = reinterpret_cast<float*>(base);
+    ex->count[peer_rank] = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(base) + ex->part_bytes);
+    return DKV_OK;
+}
+
+int dkv_exchange_destroy(dkv_exchange* ex) {
+    if (!ex) return DKV_OK;
+    cudaSetDevice(ex->ctx->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < ex->world; ++r)
+        if (ex->opened[r]) cudaIpcCloseMemHandle(ex->opened[r]);
+    if (ex->local) cudaFree(ex->local);
+    delete ex;
+    return DKV_OK;
+}
+
+int dkv_decode_exchange(dkv_context* ctx, dkv_exchange* ex, const dkv_decode_args* a, void* out, float* lse,
+                        void* stream) {
+    DKV_REQUIRE(ctx != nullptr && ex != nullptr && a != nullptr && out != nullptr, "NULL argument");
+    DKV_REQUIRE(ex->ctx == ctx, "the exchange belongs to another context");
+    for (int r = 0; r < ex->world; ++r)
+        DKV_REQUIRE(ex->part[r] != nullptr, "exchange: rank %d is not connected", r);
+    const long long rows = static_cast<long long>(a->batch) * a->nh_q;
+    DKV_REQUIRE(rows > 0 && rows <= ex->max_rows, "batch * nh_q (%lld) exceeds the exchange's max_rows (%lld)", rows,
+                ex->max_rows);
+    dkv_decode_args local = *a;
+    local.out = nullptr;
+    local.partial_out = nullptr;
+    local.lse_out = nullptr;
+    int rc = decode_impl(ctx, &local, stream, ex);
+    if (rc != DKV_OK) return rc;
+    ExchangeMergeParams ep{};
+    ep.parts = ex->part[ex->rank];
+    ep.count = ex->count[ex->rank];
+    for (int r = 0; r < ex->world; ++r) {
+        ex->expected[r] += static_cast<unsigned int>(rows);   // every rank delivers `rows` records per step
+        ep.expected[r] = ex->expected[r];
+    }
+    ep.world = ex->world;
+    ep.max_rows = ex->max_rows;
+    ep.rows = rows;
+    ep.out = static_cast<__nv_bfloat16*>(out);
+    ep.lse = lse;
+    ep.status = ctx->status;
+    merge_exchange_kernel<<<static_cast<int>((rows + 3) / 4), 128, 0, static_cast<cudaStream_t>(stream)>>>(ep);
+    DKV_CUDA(cudaGetLastError());
+    ctx->launches += 1;
+    return DKV_OK;
 }
 
 int dkv_merge_partials(dkv_context* ctx, const float* parts, int nranks, int64_t rows, void* out, float* lse,

@@ -123,8 +123,13 @@ def decode(
     partial_out: Optional[torch.Tensor] = None,  # [B, NH_q, 132] fp32: unnormalised (O, m, l)
     normalized: bool = True,
     pos_offset: Optional[torch.Tensor] = None,   # [B] int32 CUDA: added to seq_len-1 for the RoPE position
+    exchange=None,                               # handle of a connected peer-memory exchange (sharding.PartialExchange)
 ) -> Optional[torch.Tensor]:
-    """One decode step of one registered layer for a ragged batch.  Returns O with q's shape."""
+    """One decode step of one registered layer for a ragged batch.  Returns O with q's shape.
+
+    With ``exchange`` the call is this rank's part of a sequence-split decode: partial records go to
+    every rank's exchange buffer over NVLink and ``out`` is the merged result of all ranks.
+    """
     _check_cuda_bf16(q, "q")
     b = q.size(0)
     nh_q = q.numel() // (b * HEAD_DIM) if b else 0
@@ -166,7 +171,10 @@ def decode(
         lse_out=_ptr(lse_out), partial_out=_ptr(partial_out), pos_offset=_ptr(pos_offset),
     )
     ctx = get_context(q.device.index)
-    _lib.check(_lib.load().dkv_decode(ctx.handle, C.byref(a), _stream()))
+    if exchange is not None:
+        _lib.check(_lib.load().dkv_decode_exchange(ctx.handle, exchange, C.byref(a), _ptr(out), _ptr(lse_out), _stream()))
+    else:
+        _lib.check(_lib.load().dkv_decode(ctx.handle, C.byref(a), _stream()))
     return out
 
 

@@ -113,6 +113,55 @@ def all_gather_partials(part_local: torch.Tensor, group=None) -> torch.Tensor:
     return out
 
 
+class PartialExchange:
+    """Peer-memory exchange for sequence-split decode on the GPUs of one box (at most 8 ranks).
+
+    Each rank owns a device buffer ``[world, max_rows, 132]`` fp32 plus arrival counters; the buffers are
+    mapped into every rank with CUDA IPC.  A decode step then needs no collective call: the merge kernel
+    stores its partial records into every rank's buffer (plain stores over NVLink) and bumps that rank's
+    counter; a second kernel waits - with a time limit - for all sources and merges from local memory.
+    Every rank must make the same sequence of ``decode`` calls with the same ``B * NH_q``.
+    """
+
+    def __init__(self, max_rows: int, device: int, group=None):
+        import ctypes as C
+
+        from . import _lib
+
+        self._lib = _lib
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.ctx = _lib.get_context(device)
+        h = C.c_void_p()
+        _lib.check(_lib.load().dkv_exchange_create(self.ctx.handle, self.rank, self.world, int(max_rows), C.byref(h)))
+        self.handle = h
+        mine = C.create_string_buffer(64)
+        _lib.check(_lib.load().dkv_exchange_handle(self.handle, mine))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(mine.raw), group=group)
+        for r, hb in enumerate(handles):
+            if r != self.rank:
+                _lib.check(_lib.load().dkv_exchange_connect(self.handle, r, hb))
+        dist.barrier(group=group)
+
+    def decode(self, layer_id, q, local_seq_lens, softmax_scale, page_table, x=None, row_map=None, pos_offset=None,
+               lse_out=None) -> torch.Tensor:
+        """This rank's part of the step; returns the merged output ``[B, NH_q, 128]`` (same on every rank)."""
+        from . import kernel
+
+        out = kernel.decode(layer_id, q, local_seq_lens, softmax_scale, page_table=page_table, row_map=row_map, x=x,
+                            pos_offset=pos_offset, lse_out=lse_out, exchange=self.handle)
+        return out.view(q.size(0), -1, 128)
+
+    def close(self) -> None:
+        if self.handle:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)      # nobody unmaps while a peer may still be storing
+            self._lib.load().dkv_exchange_destroy(self.handle)
+            self.handle = None
+
+
 def sequence_split_decode(
     layer_id: int,
     q: torch.Tensor,                       # [B, NH_q, 128] bf16 CUDA, replicated on every rank

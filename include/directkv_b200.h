@@ -149,6 +149,25 @@ int dkv_merge_partials(dkv_context* ctx, const float* parts, int nranks, int64_t
                        void* stream);
 
 /*
+ * Sequence split with the exchange fused into the kernels (no collective call).  Each rank creates an
+ * exchange, passes its 64-byte handle to the other ranks of the box (any side channel), and connects to
+ * theirs.  dkv_decode_exchange then runs the rank's part of the decode: its merge kernel stores the
+ * unnormalised (O, m, l) record of every (request, head) row straight into every rank's exchange buffer -
+ * plain stores over NVLink for peers - and bumps a per-source arrival counter there; a second kernel waits
+ * (bounded) until all sources have delivered and merges from this GPU's own memory into out [batch, nh_q,
+ * 128] bf16 (and lse).  All ranks must call it the same number of times with the same batch * nh_q.
+ * No counterpart in the reference (which is single-GPU); the NCCL form is dkv_decode(partial_out) +
+ * all-gather + dkv_merge_partials.
+ */
+typedef struct dkv_exchange dkv_exchange;
+int dkv_exchange_create(dkv_context* ctx, int rank, int world, int64_t max_rows, dkv_exchange** out);
+int dkv_exchange_handle(dkv_exchange* ex, void* handle_out_64_bytes);
+int dkv_exchange_connect(dkv_exchange* ex, int peer_rank, const void* handle_64_bytes);
+int dkv_exchange_destroy(dkv_exchange* ex);
+int dkv_decode_exchange(dkv_context* ctx, dkv_exchange* ex, const dkv_decode_args* args, void* out, float* lse,
+                        void* stream);
+
+/*
  * Same argument meaning as the reference's smpv2_fwd(X, Wk, Wv, Q, K_cpu, V_cpu, cos_sin,
  * softmax_scale, is_causal, seqlen_past, q_pos_start) -> O
  * (directkv/kernel/smpv2_extension.cu:574-637): projects the S_new new rows, rotates K at

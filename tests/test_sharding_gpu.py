@@ -66,6 +66,18 @@ def _worker(rank, world, port):
             pos_offset=torch.tensor([s], dtype=torch.int32, device=dev) if is_owner else None)
         get_context(rank).raise_on_status()
         assert_close(o, ref1, f"sequence-split O (rank {rank})")
+        # ---- the same split with the exchange fused into the kernels (peer stores over NVLink, no NCCL call) ----
+        ex = sharding.PartialExchange(max_rows=64, device=rank)
+        lens_dev = torch.tensor([e - s], dtype=torch.int32, device=dev)
+        off_dev = torch.tensor([s], dtype=torch.int32, device=dev)
+        for it in range(3):                                   # repeated steps exercise the cumulative counters
+            lse = torch.empty(shape.nh_q, dtype=torch.float32, device=dev)
+            o2 = ex.decode(1, one["q"].to(dev), lens_dev, shape.scale, local_pages.to(dev),
+                           x=one["x"].to(dev) if is_owner else None, pos_offset=off_dev if is_owner else None, lse_out=lse)
+            torch.cuda.synchronize()
+            get_context(rank).raise_on_status()
+            assert_close(o2, ref1, f"exchange O (rank {rank}, step {it})")
+        ex.close()
     finally:
         dist.destroy_process_group()
 
