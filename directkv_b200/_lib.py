@@ -118,6 +118,8 @@ SIGNATURES = {
     "dkv_exchange_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.POINTER(C.c_void_p)]),
     "dkv_exchange_handle": (C.c_int, [C.c_void_p, C.c_char_p]),
     "dkv_exchange_connect": (C.c_int, [C.c_void_p, C.c_int, C.c_char_p]),
+    "dkv_exchange_base": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "dkv_exchange_connect_ptr": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
     "dkv_exchange_destroy": (C.c_int, [C.c_void_p]),
     "dkv_decode_exchange": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(DecodeArgs), C.c_void_p, C.c_void_p, C.c_void_p]),
     "dkv_merge_partials": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),

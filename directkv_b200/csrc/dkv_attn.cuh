@@ -559,6 +559,7 @@ struct ExchangeMergeParams {
     __nv_bfloat16* out;                       // [rows, 128]
     float* lse;                               // [rows] or nullptr
     unsigned int* status;
+    unsigned long long wait_limit_ns;         // after this long without all records the kernel reports and returns
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
@@ -579,7 +580,7 @@ __global__ void __launch_bounds__(128) merge_exchange_kernel(const ExchangeMerge
             const unsigned long long t0 = globaltimer_ns();
             for (;;) {
                 if (static_cast<int>(ld_acquire_sys(ep.count + lane) - ep.expected[lane]) >= 0) break;
-                if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                if (globaltimer_ns() - t0 > ep.wait_limit_ns) {
                     ok = false;
                     break;
                 }

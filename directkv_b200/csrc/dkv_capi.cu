@@ -118,6 +118,7 @@ struct dkv_context {
     int attn_variant = -1;              // -1: chosen per call from the head grouping
     int attn_ctas = 0;
     int proj_split_k = 0;
+    int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
     // Profiling: kernel launches issued, and CUDA-event pairs around the streaming kernel.
     long long launches = 0;
     int profile_attn = 0;
@@ -540,6 +541,9 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "attn_ctas")) {
         DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
         ctx->attn_ctas = value;
+    } else if (!strcmp(key, "wait_limit_ms")) {
+        DKV_REQUIRE(value >= 1 && value <= 60000, "wait_limit_ms must be 1..60000");
+        ctx->wait_limit_ms = value;
     } else if (!strcmp(key, "profile_attn")) {
         ctx->profile_attn = value ? 1 : 0;
     } else if (!strcmp(key, "proj_split_k")) {
@@ -766,6 +770,20 @@ int dkv_exchange_connect(dkv_exchange* ex, int peer_rank, const void* handle_64_
     return DKV_OK;
 }
 
+int dkv_exchange_connect_ptr(dkv_exchange* ex, int peer_rank, void* peer_base) {
+    DKV_REQUIRE(ex != nullptr && peer_base != nullptr, "NULL argument");
+    DKV_REQUIRE(peer_rank >= 0 && peer_rank < ex->world && peer_rank != ex->rank, "bad peer rank %d", peer_rank);
+    ex->part[peer_rank] = reinterpret_cast<float*>(peer_base);
+    ex->count[peer_rank] = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(peer_base) + ex->part_bytes);
+    return DKV_OK;
+}
+
+int dkv_exchange_base(dkv_exchange* ex, void** base_out) {
+    DKV_REQUIRE(ex != nullptr && base_out != nullptr, "NULL argument");
+    *base_out = ex->local;
+    return DKV_OK;
+}
+
 int dkv_exchange_destroy(dkv_exchange* ex) {
     if (!ex) return DKV_OK;
     cudaSetDevice(ex->ctx->device);
@@ -805,6 +823,7 @@ int dkv_decode_exchange(dkv_context* ctx, dkv_exchange* ex, const dkv_decode_arg
     ep.out = static_cast<__nv_bfloat16*>(out);
     ep.lse = lse;
     ep.status = ctx->status;
+    ep.wait_limit_ns = static_cast<unsigned long long>(ctx->wait_limit_ms) * 1000000ull;
     merge_exchange_kernel<<<static_cast<int>((rows + 3) / 4), 128, 0, static_cast<cudaStream_t>(stream)>>>(ep);
     DKV_CUDA(cudaGetLastError());
     ctx->launches += 1;

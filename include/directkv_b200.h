@@ -65,7 +65,8 @@ int dkv_context_destroy(dkv_context* ctx);
 int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv, int hidden);
 
 /* Knobs, by name: "attn_variant" (-1 = automatic, 0..2), "attn_ctas" (CTAs of the streaming kernel,
- * 0 = one per SM), "proj_split_k" (0 = automatic), "profile_attn" (0/1, see dkv_profile_read). */
+ * 0 = one per SM), "proj_split_k" (0 = automatic), "profile_attn" (0/1, see dkv_profile_read), "wait_limit_ms" (how long
+ * dkv_decode_exchange's consumer kernel waits for its peers before it reports DKV_STATUS_WAIT_TIMEOUT; 2000). */
 int dkv_context_set(dkv_context* ctx, const char* key, int value);
 
 /*
@@ -163,6 +164,10 @@ typedef struct dkv_exchange dkv_exchange;
 int dkv_exchange_create(dkv_context* ctx, int rank, int world, int64_t max_rows, dkv_exchange** out);
 int dkv_exchange_handle(dkv_exchange* ex, void* handle_out_64_bytes);
 int dkv_exchange_connect(dkv_exchange* ex, int peer_rank, const void* handle_64_bytes);
+/* Same-process form (one process driving several GPUs with peer access enabled, or several logical ranks on
+ * one GPU): the peer's buffer address instead of an IPC handle. */
+int dkv_exchange_base(dkv_exchange* ex, void** base_out);
+int dkv_exchange_connect_ptr(dkv_exchange* ex, int peer_rank, void* peer_base);
 int dkv_exchange_destroy(dkv_exchange* ex);
 int dkv_decode_exchange(dkv_context* ctx, dkv_exchange* ex, const dkv_decode_args* args, void* out, float* lse,
                         void* stream);
