@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "dkv_attn.cuh"
+#include "dkv_extend.cuh"
 #include "dkv_proj.cuh"
 
 namespace {
@@ -89,16 +90,34 @@ int encode_operand_map(CUtensorMap* m, const void* base, int64_t rows, int64_t c
     return DKV_OK;
 }
 
+// [rows, nh, 128] bf16 as a 3-D map (d, head, row); box = 64 columns x `box_heads` x `box_rows`, 128-byte swizzle:
+// the operand tiles of the tensor-core extend kernel (K/V: one head, 128 rows; Q: G heads of 128/G tokens).
+int encode_tile_map(CUtensorMap* m, const void* base, int64_t rows, int nh, int box_heads, int box_rows) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) return fail(DKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    cuuint64_t gdim[3] = {128, (cuuint64_t)nh, (cuuint64_t)rows};
+    cuuint64_t gstr[2] = {256, (cuuint64_t)nh * 256};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), gdim, gstr, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DKV_ERR_CUDA, "cuTensorMapEncodeTiled(tile) failed: %d", (int)r);
+    return DKV_OK;
+}
+
 struct LayerState {
     dkv_layer_desc d{};
     void* k_dev = nullptr;  // device-visible address of the pool
     void* v_dev = nullptr;
     CUtensorMap tmK_page{}, tmV_page{};  // box rows = min(16, page_size)
     CUtensorMap tmK_16{}, tmV_16{};      // box rows = 16 (contiguous rows)
+    CUtensorMap tmK_128{}, tmV_128{};    // 128 rows x 64 columns, 128-byte swizzle (tensor-core extend)
     CUtensorMap tmWk{}, tmWv{};
     int page_shift = 0;
     int rows_per_box = 16;
     bool has_weights = false;
+    bool pool_on_host = false;
 };
 
 constexpr int kMaxCounters = 4096;
@@ -119,6 +138,7 @@ struct dkv_context {
     int attn_ctas = 0;
     int proj_split_k = 0;
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
+    int extend_rowwise = 0;             // 1: extend attends row by row with the decode kernels (reference path for tests)
     // Profiling: kernel launches issued, and CUDA-event pairs around the streaming kernel.
     long long launches = 0;
     int profile_attn = 0;
@@ -222,6 +242,25 @@ __global__ void __launch_bounds__(128) scatter_rows_kernel(uint4* __restrict__ d
     for (int c = threadIdx.x; c < row_vec; c += blockDim.x) dst[slot * row_vec + c] = src[i * row_vec + c];
 }
 
+// Extend over a host pool: rows [0, s_total) of every request are brought into a device staging tensor
+// [B, s_total, nh, 128] ONCE (16-byte read-only loads over the host link), so that the tensor-core kernel,
+// which visits the keys once per 128-row query tile, re-reads them from HBM/L2 and not over PCIe.
+__global__ void __launch_bounds__(256) stage_rows_kernel(uint4* __restrict__ k_dst, uint4* __restrict__ v_dst,
+                                                         const uint4* __restrict__ k_src, const uint4* __restrict__ v_src,
+                                                         const int* __restrict__ row_map, long long row_stride, int B,
+                                                         int s_total, int row_vec /* nh * 16 */) {
+    const long long per_req = static_cast<long long>(s_total) * row_vec;
+    const long long total = per_req * B;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int b = static_cast<int>(i / per_req);
+        const long long r = i - b * per_req;
+        const long long src = static_cast<long long>(row_map ? row_map[b] : b) * row_stride * row_vec + r;
+        k_dst[i] = __ldg(k_src + src);
+        v_dst[i] = __ldg(v_src + src);
+    }
+}
+
 // Plain streaming copy (16-byte read-only loads), for measuring what SM-issued reads of
 // host-mapped memory reach on this machine's host link.
 __global__ void __launch_bounds__(256) stream_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src,
@@ -274,7 +313,7 @@ constexpr size_t kProjSmem = static_cast<size_t>(kProjStages) * kProjStage + 409
 size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
 struct ScratchPlan {
-    size_t cum, tok_pos, tok_slot, vseq, vrow, partials, kv_new, splitk, q_rot, total;
+    size_t cum, tok_pos, tok_slot, vseq, vrow, partials, kv_new, splitk, q_rot, stage_k, stage_v, total;
 };
 
 int choose_g(int g_total) { return (g_total % 4 == 0) ? 4 : (g_total % 2 == 0) ? 2 : 1; }
@@ -305,7 +344,7 @@ void proj_split(const dkv_context* ctx, int T, int nh_kv, int H, int* split_k, i
 }
 
 ScratchPlan plan_scratch(const dkv_context* ctx, int64_t rows, int nh_q, int nh_kv, int hidden, bool with_proj,
-                         bool with_qrot) {
+                         bool with_qrot, size_t stage_bytes = 0) {
     ScratchPlan s{};
     const int g_total = nh_q / nh_kv;
     const int G = choose_g(g_total);
@@ -330,6 +369,11 @@ ScratchPlan plan_scratch(const dkv_context* ctx, int64_t rows, int nh_q, int nh_
     }
     s.q_rot = off;
     if (with_qrot) off += align256(static_cast<size_t>(rows) * nh_q * 128 * 2);
+    off = (off + 1023) & ~static_cast<size_t>(1023);
+    s.stage_k = off;
+    off += align256(stage_bytes);
+    s.stage_v = off;
+    off += align256(stage_bytes);
     s.total = off;
     return s;
 }
@@ -371,6 +415,11 @@ int build_layer(LayerState* L, const dkv_layer_desc* d) {
                 "KV pool base addresses must be 16-byte aligned");
     L->d = *d;
     int rc;
+    {
+        cudaPointerAttributes attr;
+        DKV_CUDA(cudaPointerGetAttributes(&attr, d->k_pool));
+        L->pool_on_host = (attr.type == cudaMemoryTypeHost);
+    }
     if ((rc = device_pointer_of(d->k_pool, &L->k_dev, "k_pool")) != DKV_OK) return rc;
     if ((rc = device_pointer_of(d->v_pool, &L->v_dev, "v_pool")) != DKV_OK) return rc;
     L->page_shift = 0;
@@ -380,6 +429,8 @@ int build_layer(LayerState* L, const dkv_layer_desc* d) {
     if ((rc = encode_pool_map(&L->tmV_page, L->v_dev, d->n_slots, d->nh_kv, L->rows_per_box)) != DKV_OK) return rc;
     if ((rc = encode_pool_map(&L->tmK_16, L->k_dev, d->n_slots, d->nh_kv, kTileTokens)) != DKV_OK) return rc;
     if ((rc = encode_pool_map(&L->tmV_16, L->v_dev, d->n_slots, d->nh_kv, kTileTokens)) != DKV_OK) return rc;
+    if ((rc = encode_tile_map(&L->tmK_128, L->k_dev, d->n_slots, d->nh_kv, 1, kExtTile)) != DKV_OK) return rc;
+    if ((rc = encode_tile_map(&L->tmV_128, L->v_dev, d->n_slots, d->nh_kv, 1, kExtTile)) != DKV_OK) return rc;
     L->has_weights = (d->wk != nullptr && d->wv != nullptr);
     if (L->has_weights) {
         DKV_REQUIRE(d->hidden > 0 && d->hidden % kProjBK == 0, "hidden (%d) must be a positive multiple of 64", d->hidden);
@@ -497,6 +548,8 @@ int dkv_context_create(int device, dkv_context** out) {
     if (e == cudaSuccess) e = attn_set_attr<1, 16, 1>();
     if (e == cudaSuccess) e = attn_set_attr<2, 16, 1>();
     if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(extend_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kExtSmem + 1024);
+    if (e == cudaSuccess)
         e = cudaFuncSetAttribute(proj_rope_kernel<kProjStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kProjSmem));
     if (e != cudaSuccess) {
@@ -541,6 +594,8 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "attn_ctas")) {
         DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
         ctx->attn_ctas = value;
+    } else if (!strcmp(key, "extend_rowwise")) {
+        ctx->extend_rowwise = value ? 1 : 0;
     } else if (!strcmp(key, "wait_limit_ms")) {
         DKV_REQUIRE(value >= 1 && value <= 60000, "wait_limit_ms must be 1..60000");
         ctx->wait_limit_ms = value;
@@ -848,7 +903,12 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
     const int nh_kv = L.d.nh_kv;
     const int64_t rows = static_cast<int64_t>(B) * S_new;
     const bool qrot = (L.d.cos_sin != nullptr && q_pos_start >= 0);
-    ScratchPlan sp = plan_scratch(ctx, rows, nh_q, nh_kv, L.d.hidden, true, qrot);
+    // Host pool, length known on the host, more than one query tile: stage the rows in HBM once.
+    const int s_total_host = seqlen_past + S_new;
+    const bool stage = !ctx->extend_rowwise && L.pool_on_host && n_past_blocks_dev == nullptr &&
+                       static_cast<long long>(S_new) * (nh_q / nh_kv) > kExtTile;
+    const size_t stage_bytes = stage ? static_cast<size_t>(B) * s_total_host * nh_kv * 256 : 0;
+    ScratchPlan sp = plan_scratch(ctx, rows, nh_q, nh_kv, L.d.hidden, true, qrot, stage_bytes);
     int rc = ensure_scratch(ctx, sp.total);
     if (rc != DKV_OK) return rc;
     uint8_t* base = ctx->scratch;
@@ -880,6 +940,58 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
                                                                            L.d.max_pos, q_pos_start, ctx->status);
         DKV_CUDA(cudaGetLastError());
         q_use = q_rot;
+    }
+    if (!ctx->extend_rowwise) {
+        // Tensor-core path: 128 query rows per CTA = G query heads x 128/G tokens of one KV head.
+        const int g_total = nh_q / nh_kv;
+        int G = 1;
+        while (G < 128 && g_total % (2 * G) == 0) G *= 2;
+        const int nsub = g_total / G;
+        const int TQ = kExtTile / G;
+        CUtensorMap tmQ;
+        rc = encode_tile_map(&tmQ, q_use, rows, nh_q, G, TQ);
+        if (rc != DKV_OK) return rc;
+        const CUtensorMap* tmK = &L.tmK_128;
+        const CUtensorMap* tmV = &L.tmV_128;
+        CUtensorMap tmKs, tmVs;
+        const int32_t* ext_rows = row_map;
+        long long ext_stride = L.d.row_stride;
+        if (stage) {
+            uint4* ks = reinterpret_cast<uint4*>(base + sp.stage_k);
+            uint4* vs = reinterpret_cast<uint4*>(base + sp.stage_v);
+            stage_rows_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(ks, vs, static_cast<const uint4*>(L.k_dev),
+                                                                 static_cast<const uint4*>(L.v_dev), row_map,
+                                                                 L.d.row_stride, B, s_total_host, nh_kv * 16);
+            DKV_CUDA(cudaGetLastError());
+            ctx->launches += 1;
+            const int64_t srows = static_cast<int64_t>(B) * s_total_host;
+            if ((rc = encode_tile_map(&tmKs, ks, srows, nh_kv, 1, kExtTile)) != DKV_OK) return rc;
+            if ((rc = encode_tile_map(&tmVs, vs, srows, nh_kv, 1, kExtTile)) != DKV_OK) return rc;
+            tmK = &tmKs;
+            tmV = &tmVs;
+            ext_rows = nullptr;
+            ext_stride = s_total_host;
+        }
+        ExtendParams ep{};
+        ep.vrow = ext_rows;
+        ep.n_past_blocks = n_past_blocks_dev;
+        ep.seqlen_past = seqlen_past;
+        ep.S_new = S_new;
+        ep.nh_q = nh_q;
+        ep.nh_kv = nh_kv;
+        ep.G = G;
+        ep.g_total = g_total;
+        ep.nsub = nsub;
+        ep.row_stride = ext_stride;
+        ep.is_causal = is_causal;
+        ep.scale_log2 = scale * 1.4426950408889634f;
+        ep.out = static_cast<__nv_bfloat16*>(O);
+        ep.status = ctx->status;
+        dim3 grid((S_new + TQ - 1) / TQ, nh_kv * nsub, B);
+        extend_attn_kernel<<<grid, 128, kExtSmem + 1024, st>>>(tmQ, *tmK, *tmV, ep);
+        DKV_CUDA(cudaGetLastError());
+        ctx->launches += 1;
+        return DKV_OK;
     }
     AttnParams ap{};
     ap.q = q_use;

@@ -147,3 +147,32 @@ def test_graph_entry_points_replay():
     get_context(0).raise_on_status()
     assert_close(O, ref2, "replayed O")
     kernel.unregister_layer(50)
+
+
+@pytest.mark.parametrize("nh_q,nh_kv,S_new,S_past,host", [
+    (32, 8, 600, 1000, True),      # Llama-3-8B grouping: 4 query heads x 32 tokens per CTA, staged host pool
+    (8, 8, 300, 0, True),          # MHA, first chunk
+    (16, 1, 130, 70, False),       # 16 query heads on one KV head: 8 tokens per CTA
+    (12, 2, 200, 333, True),       # ratio 6 = 2 x 3 sub-groups
+    (4, 4, 128, 128, False),       # exactly one tile of each
+])
+def test_tensor_core_extend_shapes(nh_q, nh_kv, S_new, S_past, host):
+    X, Wk, Wv, Q, K, V, cs = _rand_case(2, nh_q, nh_kv, S_new, S_past, 256, seed=900 + S_new)
+    _run_fwd(X, Wk, Wv, Q, K, V, cs, True, S_past, kv_on_host=host)
+
+
+def test_extend_paths_agree():
+    """The tensor-core extend kernel and the row-streamed path (decode kernels, one virtual request per new
+    row) implement the same function: compare them directly, non-causal included."""
+    ctx = get_context(0)
+    for causal in (True, False):
+        X, Wk, Wv, Q, K, V, cs = _rand_case(1, 8, 2, 257, 100, 128, seed=31)
+        outs = []
+        for rowwise in (0, 1):
+            ctx.set("extend_rowwise", rowwise)
+            Kd, Vd = K.clone().pin_memory(), V.clone().pin_memory()
+            outs.append(kernel.smpv2_fwd(X.to(DEV), Wk.to(DEV), Wv.to(DEV), Q.to(DEV), Kd, Vd, cs.to(DEV), SCALE, causal,
+                                         100, -1).float().cpu())
+        ctx.set("extend_rowwise", 0)
+        ctx.raise_on_status()
+        assert (outs[0] - outs[1]).abs().max() < 2e-2
