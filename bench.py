@@ -205,6 +205,33 @@ def _oracle_error(case, shape, lens, page, out, pick):
     return float(err.max()), float((err / ref[0].abs().clamp_min(1e-2)).max())
 
 
+def run_extend_probe(args, dev):
+    """Chunked-prefill path (projection + RoPE + write-back + tensor-core attention) of one Llama-3-8B layer:
+    4096 new tokens, no past, KV pool in HBM.  Prints attention TFLOP/s (causal flops only)."""
+    from directkv_b200 import kernel
+    from directkv_b200._lib import get_context
+
+    shape, s_new = workloads.LLAMA3_8B, 4096
+    g = torch.Generator(device=dev).manual_seed(1234)
+    x = torch.randn(1, s_new, shape.hidden, generator=g, device=dev).to(torch.bfloat16)
+    wk = (torch.randn(shape.nh_kv, 128, shape.hidden, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    wv = (torch.randn(shape.nh_kv, 128, shape.hidden, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    q = torch.randn(1, s_new, shape.nh_q, 128, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.zeros(1, s_new, shape.nh_kv, 128, dtype=torch.bfloat16, device=dev)
+    v = torch.zeros_like(k)
+    cs = workloads.build_cos_sin(s_new, shape.rope_theta, device=dev)
+
+    def fn():
+        kernel.smpv2_fwd(x, wk, wv, q, k, v, cs, shape.scale, True, 0, -1)
+
+    med, best = _median_ms(fn, max(3, min(args.steps, 20)), args.warmup, torch.cuda.synchronize)
+    get_context(dev.index).raise_on_status()
+    flops = 4 * 128 * shape.nh_q * s_new * (s_new + 1) / 2
+    print(json.dumps({"metric": "extend_attention_tflops", "value": flops / med / 1e9, "unit": "TFLOP/s",
+                      "ms_per_step": med, "config": {"workload": "llama3-8b layer, 4096 new tokens, causal, KV in HBM"},
+                      "partial": "extend path only"}))
+
+
 def run_sweep(args, rank, world, local_rank, dev, dist):
     from directkv_b200 import kernel, sharding
     from directkv_b200._lib import get_context
@@ -331,6 +358,8 @@ def run_sweep(args, rank, world, local_rank, dev, dist):
                 if world > 1 and n < 1048576:
                     continue
                 seq_split(f"C3 llama3-8b x32 layers ctx {n}", n, 2)
+        elif name == "L128K":      # GQA streaming kernel at HBM speed: one Llama-3-8B request of 128K tokens
+            one_layer("llama3-8b B=1 ctx 131072", workloads.LLAMA3_8B, [131073], 2, modes=("hbm",), iters=50)
         elif name == "C4":
             base = workloads.ragged_lengths_lognormal(64, 8192, 1.0, 256, 131072, seed=4234 + 3)
             g = torch.Generator().manual_seed(99)
@@ -359,8 +388,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--variant", type=int, default=None, help="override the streaming-kernel variant")
-    ap.add_argument("--only", default="all", choices=["all", "hbm", "host"],
-                    help="hbm / host: time only that mode (short runs for profiler captures)")
+    ap.add_argument("--only", default="all", choices=["all", "hbm", "host", "extend"],
+                    help="hbm / host: time only that mode of the decode step; extend: time the chunked-prefill path "
+                         "(Llama-3-8B layer, 4096 new tokens) - short runs for profiler captures")
     ap.add_argument("--sweep", default=None, help="comma list of C1,C2,C3,C4,C5: run those configurations instead")
     ap.add_argument("--sweep-out", default="gpurun_out/sweep.jsonl")
     args = ap.parse_args()
@@ -408,6 +438,10 @@ def main():
         t = torch.tensor([x], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
+
+    if args.only == "extend":
+        run_extend_probe(args, dev)
+        return
 
     shape = workloads.OPT_6_7B
     lens = c2_lengths(rank)

@@ -180,6 +180,20 @@ __device__ __forceinline__ void issue_tile(const AttnParams& p, const CUtensorMa
     }
 }
 
+// Pair-wise fp32 math.  With one or two query heads per KV head the packed two-wide FMA of sm_100 halves the
+// FMA instruction count; with four, the register pairing it needs costs more than it saves (measured), so
+// the components are computed separately there.
+template <bool PACKED>
+__device__ __forceinline__ float2 fma2(const float2 a, const float2 b, const float2 c) {
+    if constexpr (PACKED) return __ffma2_rn(a, b, c);
+    else return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
+}
+template <bool PACKED>
+__device__ __forceinline__ float2 mul2(const float2 a, const float2 b) {
+    if constexpr (PACKED) return __fmul2_rn(a, b);
+    else return make_float2(a.x * b.x, a.y * b.y);
+}
+
 // ---------------------------------------------------------------------------
 // Partial attention.  Lane (g4 = lane / 8, j = lane % 8) owns tokens t == g4 (mod 4) of each
 // tile and the head-dim slices [8j, 8j+8) and [64+8j, 64+8j+8); a quarter-warp therefore reads
@@ -232,8 +246,9 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     int stage = 0;
     bool failed = false;
 
-    float qf[G][16];
-    float O[G][16];
+    // fp32 pairs: the math below uses the packed two-wide FMA of sm_100 (one instruction per pair).
+    float2 qf[G][8];
+    float2 O[G][8];
     float m[G], l[G];
     int past_b = 0;
     bool seg_open = false;
@@ -251,11 +266,10 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                 const uint32_t w[8] = {a.x, a.y, a.z, a.w, b2.x, b2.y, b2.z, b2.w};
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    qf[g][2 * i] = bf16lo(w[i]) * p.scale_log2;
-                    qf[g][2 * i + 1] = bf16hi(w[i]) * p.scale_log2;
+                    qf[g][i] = make_float2(bf16lo(w[i]) * p.scale_log2, bf16hi(w[i]) * p.scale_log2);
                 }
 #pragma unroll
-                for (int i = 0; i < 16; ++i) O[g][i] = 0.f;
+                for (int i = 0; i < 8; ++i) O[g][i] = make_float2(0.f, 0.f);
                 m[g] = -INFINITY;
                 l[g] = 0.f;
             }
@@ -282,21 +296,18 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             const uint4 ka = *reinterpret_cast<const uint4*>(sK + t * kRowBytes + 16 * j);
             const uint4 kb = *reinterpret_cast<const uint4*>(sK + t * kRowBytes + 128 + 16 * j);
             const uint32_t w[8] = {ka.x, ka.y, ka.z, ka.w, kb.x, kb.y, kb.z, kb.w};
-            float kf[16];
+            float2 kf[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                kf[2 * i] = bf16lo(w[i]);
-                kf[2 * i + 1] = bf16hi(w[i]);
-            }
+            for (int i = 0; i < 8; ++i) kf[i] = make_float2(bf16lo(w[i]), bf16hi(w[i]));
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                float a0 = 0.f, a1 = 0.f;
+                float2 a0 = make_float2(0.f, 0.f), a1 = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    a0 = fmaf(qf[g][i], kf[i], a0);
-                    a1 = fmaf(qf[g][i + 1], kf[i + 1], a1);
+                for (int i = 0; i < 8; i += 2) {
+                    a0 = fma2<(G <= 2)>(qf[g][i], kf[i], a0);
+                    a1 = fma2<(G <= 2)>(qf[g][i + 1], kf[i + 1], a1);
                 }
-                float acc = a0 + a1;
+                float acc = (a0.x + a0.y) + (a1.x + a1.y);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 1);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 2);
                 acc += __shfl_xor_sync(0xffffffffu, acc, 4);
@@ -323,7 +334,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             l[g] = l[g] * alpha + ps;
             m[g] = m_new;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) O[g][i] *= alpha;
+            for (int i = 0; i < 8; ++i) O[g][i] = mul2<(G <= 2)>(O[g][i], make_float2(alpha, alpha));
         }
 
         // ---- O += P . V ----
@@ -336,12 +347,9 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                 const uint32_t w[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const float v0 = bf16lo(w[i]), v1 = bf16hi(w[i]);
+                    const float2 v2 = make_float2(bf16lo(w[i]), bf16hi(w[i]));
 #pragma unroll
-                    for (int g = 0; g < G; ++g) {
-                        O[g][2 * i] = fmaf(pr[g][tt], v0, O[g][2 * i]);
-                        O[g][2 * i + 1] = fmaf(pr[g][tt], v1, O[g][2 * i + 1]);
-                    }
+                    for (int g = 0; g < G; ++g) O[g][i] = fma2<(G <= 2)>(make_float2(pr[g][tt], pr[g][tt]), v2, O[g][i]);
                 }
             }
         }
@@ -366,19 +374,21 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
                 lt += __shfl_xor_sync(0xffffffffu, lt, 8);
                 lt += __shfl_xor_sync(0xffffffffu, lt, 16);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float o = O[g][i];
-                    o += __shfl_xor_sync(0xffffffffu, o, 8);
-                    o += __shfl_xor_sync(0xffffffffu, o, 16);
+                for (int i = 0; i < 8; ++i) {
+                    float2 o = O[g][i];
+                    o.x += __shfl_xor_sync(0xffffffffu, o.x, 8);
+                    o.y += __shfl_xor_sync(0xffffffffu, o.y, 8);
+                    o.x += __shfl_xor_sync(0xffffffffu, o.x, 16);
+                    o.y += __shfl_xor_sync(0xffffffffu, o.y, 16);
                     O[g][i] = o;
                 }
                 if (g4 == 0) {
                     float* og = out + g * kPartialStride;
-                    *reinterpret_cast<float4*>(og + 8 * j) = make_float4(O[g][0], O[g][1], O[g][2], O[g][3]);
-                    *reinterpret_cast<float4*>(og + 8 * j + 4) = make_float4(O[g][4], O[g][5], O[g][6], O[g][7]);
-                    *reinterpret_cast<float4*>(og + 64 + 8 * j) = make_float4(O[g][8], O[g][9], O[g][10], O[g][11]);
+                    *reinterpret_cast<float4*>(og + 8 * j) = make_float4(O[g][0].x, O[g][0].y, O[g][1].x, O[g][1].y);
+                    *reinterpret_cast<float4*>(og + 8 * j + 4) = make_float4(O[g][2].x, O[g][2].y, O[g][3].x, O[g][3].y);
+                    *reinterpret_cast<float4*>(og + 64 + 8 * j) = make_float4(O[g][4].x, O[g][4].y, O[g][5].x, O[g][5].y);
                     *reinterpret_cast<float4*>(og + 64 + 8 * j + 4) =
-                        make_float4(O[g][12], O[g][13], O[g][14], O[g][15]);
+                        make_float4(O[g][6].x, O[g][6].y, O[g][7].x, O[g][7].y);
                     if (j == 0) {
                         og[128] = m[g];
                         og[129] = lt;

