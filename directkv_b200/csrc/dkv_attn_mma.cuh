@@ -1,0 +1,301 @@
+// Streaming split-KV decode attention for grouped queries (3..16 query heads per KV head).
+//
+// Same work decomposition, cursors, partial records and merge as dkv_attn.cuh; only the inner product
+// differs.  With G query heads sharing a KV head the per-byte arithmetic (G FMAs per bf16 element) makes
+// the CUDA-core kernel issue-bound at G = 4, so here the G query rows form the (zero-padded) 16-row M side
+// of warp-level tensor-core products:
+//
+//   S[16 x 16 tokens] = Q[16 x 128] . K_tile^T      8 k-steps x 2 token halves  = 16 mma.m16n8k16
+//   O[16 x 128]      += P[16 x 16]  . V_tile        16 head-dim slices          = 16 mma.m16n8k16
+//
+// K and V tiles come by TMA as two 64-column boxes with the 128-byte swizzle, which makes every ldmatrix
+// (plain for K, transposed for V) conflict-free; the S accumulators are already laid out as the A operand
+// of the second product, so probabilities go from registers to the tensor core without a shuffle.
+// Scores, maxima and sums stay fp32; probabilities are rounded to bf16 for the second product.
+//
+// (tcgen05 is not used here on purpose: its smallest tile is 64 rows and its accumulator lives in TMEM
+// behind a commit/wait round trip per tile; for 4..16 live rows per 16-token tile the warp-level
+// instruction is the right size.)
+#pragma once
+
+#include "dkv_attn.cuh"
+
+namespace dkv {
+
+constexpr int kMmaHalfBytes = kTileTokens * 128;   // one [16 tokens x 64 bf16] swizzled block: 2 KB
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+// D (fp32) += A (bf16, 16x16 row-major fragments) * B (bf16, 16x8 column fragments)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Byte offset of 16-byte chunk `c16` (0..15 over the 256-byte row) of token row `t` inside a K or V tile that
+// was loaded as two 128-byte-swizzled 64-column boxes.
+__device__ __forceinline__ uint32_t sw_tile_off(int t, int c16) {
+    return static_cast<uint32_t>((c16 >> 3) * kMmaHalfBytes + t * 128 + (((c16 & 7) ^ (t & 7)) << 4));
+}
+
+// Lane 0 only: TMA copies of one tile (K low/high columns, V low/high columns) into a stage laid out
+// [K lo | K hi | V lo | V hi], 2 KB each.
+__device__ __forceinline__ void issue_tile_sw(const AttnParams& p, const CUtensorMap* tmK, const CUtensorMap* tmV,
+                                              const TileCursor& c, uint8_t* stage, uint64_t* bar) {
+    const int h = c.hs / p.nsub;
+    const int tok0 = c.tile * kTileTokens;
+    const int row = p.row_map ? p.row_map[c.b] : c.b;
+    auto four = [&](int dst_row, int slot) {
+        uint8_t* d = stage + dst_row * 128;
+        tma_load_3d(d, tmK, bar, 0, h, slot);
+        tma_load_3d(d + kMmaHalfBytes, tmK, bar, 64, h, slot);
+        tma_load_3d(d + 2 * kMmaHalfBytes, tmV, bar, 0, h, slot);
+        tma_load_3d(d + 3 * kMmaHalfBytes, tmV, bar, 64, h, slot);
+    };
+    if (p.page_table == nullptr) {
+        mbar_arrive_expect_tx(bar, kStageBytes);
+        four(0, static_cast<int>(static_cast<long long>(row) * p.row_stride + tok0));
+    } else if (p.page_size >= kTileTokens) {
+        const int page = p.page_table[static_cast<long long>(row) * p.pt_stride + (tok0 >> p.page_shift)];
+        mbar_arrive_expect_tx(bar, kStageBytes);
+        four(0, static_cast<int>((static_cast<long long>(page) << p.page_shift) + (tok0 & (p.page_size - 1))));
+    } else {
+        const int past = p.seq_lens[c.b] - p.n_new;
+        const int rows = p.rows_per_box;
+        int npages = (past - tok0 + rows - 1) >> p.page_shift;
+        const int max_pages = kTileTokens >> p.page_shift;
+        npages = npages < max_pages ? npages : max_pages;
+        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(npages * rows * kRowBytes * 2));
+        const int* pt = p.page_table + static_cast<long long>(row) * p.pt_stride + (tok0 >> p.page_shift);
+        for (int r = 0; r < npages; ++r) four(r * rows, static_cast<int>(static_cast<long long>(pt[r]) << p.page_shift));
+    }
+}
+
+template <int NWARPS, int NST>
+__global__ void __launch_bounds__(NWARPS * 32, 1)
+attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                        const AttnParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r4 = lane >> 2, c4 = lane & 3;          // fragment row (and row + 8), column pair
+    uint8_t* wbase = smem + static_cast<size_t>(warp) * NST * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(NWARPS) * NST * kStageBytes) + warp * NST;
+
+    const int G = p.g_total / p.nsub;                 // query rows per record, <= 16
+    const bool hi_rows = G > 8;
+    const int nhs = p.nh_kv * p.nsub;
+    const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
+    const long long qn = (U + p.total_warps - 1) / p.total_warps;
+    const int gw = blockIdx.x * NWARPS + warp;
+    const long long u0 = static_cast<long long>(gw) * qn;
+    const long long u1 = (u0 + qn < U) ? u0 + qn : U;
+    if (u0 >= u1) return;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < NST; ++s) mbar_init(&bars[s], 1);
+        fence_mbar_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    __syncwarp();
+
+    TileCursor cc, pc;
+    cc.locate(p, u0, nhs);
+    pc = cc;
+    long long pu = u0;
+#pragma unroll
+    for (int s = 0; s < NST; ++s) {
+        if (pu < u1) {
+            if (lane == 0) issue_tile_sw(p, &tmK, &tmV, pc, wbase + s * kStageBytes, &bars[s]);
+            pc.advance(p, nhs);
+            ++pu;
+        }
+    }
+
+    uint32_t phase_bits = 0;
+    int stage = 0;
+    bool failed = false;
+
+    uint32_t qa[8][4];            // A fragments of the (zero-padded) 16 x 128 query block
+    float o[16][4];               // O accumulators: 16 slices of 8 head-dim columns
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    int past_b = 0;
+    bool seg_open = false;
+
+    for (long long u = u0; u < u1; ++u) {
+        if (!seg_open) {
+            const int h = cc.hs / p.nsub, sub = cc.hs - h * p.nsub;
+            const __nv_bfloat16* qrow =
+                p.q + static_cast<long long>(cc.b) * p.q_stride + static_cast<long long>(h * p.g_total + sub * G) * kHeadDim;
+            const bool v_lo = r4 < G, v_hi = r4 + 8 < G;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                const int d0 = ks * 16 + 2 * c4;
+                qa[ks][0] = v_lo ? *reinterpret_cast<const uint32_t*>(qrow + r4 * kHeadDim + d0) : 0u;
+                qa[ks][2] = v_lo ? *reinterpret_cast<const uint32_t*>(qrow + r4 * kHeadDim + d0 + 8) : 0u;
+                qa[ks][1] = v_hi ? *reinterpret_cast<const uint32_t*>(qrow + (r4 + 8) * kHeadDim + d0) : 0u;
+                qa[ks][3] = v_hi ? *reinterpret_cast<const uint32_t*>(qrow + (r4 + 8) * kHeadDim + d0 + 8) : 0u;
+            }
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+            m_lo = m_hi = -INFINITY;
+            l_lo = l_hi = 0.f;
+            past_b = p.seq_lens[cc.b] - p.n_new;
+            seg_open = true;
+        }
+
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bars[stage], (phase_bits >> stage) & 1u))) {
+            failed = true;
+            break;
+        }
+        phase_bits ^= (1u << stage);
+        uint8_t* sK = wbase + stage * kStageBytes;
+        uint8_t* sV = sK + 2 * kMmaHalfBytes;
+        const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV);
+        const int valid = past_b - cc.tile * kTileTokens;
+
+        if (valid < kTileTokens) {
+            // Rows past the request's last token may hold anything; their probabilities are zero, but the
+            // tensor core still multiplies, so V must be finite there.
+            for (int idx = lane; idx < (kTileTokens - valid) * 16; idx += 32)
+                *reinterpret_cast<uint4*>(sV + sw_tile_off(valid + (idx >> 4), idx & 15)) = make_uint4(0, 0, 0, 0);
+            fence_proxy_async_smem();   // these stores precede the next TMA write into the same stage
+            __syncwarp();
+        }
+
+        // ---- S = Q K^T ----
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};   // tokens 0-7, tokens 8-15
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            const int tok = (mi >> 1) * 8 + r;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t b[4];
+                ldmatrix_x4(b, sK_a + sw_tile_off(tok, 2 * ks + (mi & 1)));
+                mma_bf16_16816(s0, qa[ks], b[0], b[1]);
+                mma_bf16_16816(s1, qa[ks], b[2], b[3]);
+            }
+        }
+        // ---- online softmax: this lane holds tokens 2*c4, 2*c4+1 (s0) and 8+2*c4, 9+2*c4 (s1) of rows r4, r4+8 ----
+        const bool t0 = 2 * c4 < valid, t1 = 2 * c4 + 1 < valid, t2 = 8 + 2 * c4 < valid, t3 = 9 + 2 * c4 < valid;
+        float v_lo4[4] = {t0 ? s0[0] * p.scale_log2 : -INFINITY, t1 ? s0[1] * p.scale_log2 : -INFINITY,
+                          t2 ? s1[0] * p.scale_log2 : -INFINITY, t3 ? s1[1] * p.scale_log2 : -INFINITY};
+        float tm = fmaxf(fmaxf(v_lo4[0], v_lo4[1]), fmaxf(v_lo4[2], v_lo4[3]));
+        tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+        tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+        const float mn_lo = fmaxf(m_lo, tm);
+        const float mu_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo;
+        const float alpha_lo = exp2f(m_lo - mu_lo);
+        const float p0 = exp2f(v_lo4[0] - mu_lo), p1 = exp2f(v_lo4[1] - mu_lo), p2 = exp2f(v_lo4[2] - mu_lo),
+                    p3 = exp2f(v_lo4[3] - mu_lo);
+        l_lo = l_lo * alpha_lo + (p0 + p1) + (p2 + p3);
+        m_lo = mn_lo;
+        uint32_t pa[4];
+        pa[0] = pack_bf16x2(p0, p1);
+        pa[2] = pack_bf16x2(p2, p3);
+        pa[1] = 0u;
+        pa[3] = 0u;
+        float alpha_hi = 1.f;
+        if (hi_rows) {
+            float w4[4] = {t0 ? s0[2] * p.scale_log2 : -INFINITY, t1 ? s0[3] * p.scale_log2 : -INFINITY,
+                           t2 ? s1[2] * p.scale_log2 : -INFINITY, t3 ? s1[3] * p.scale_log2 : -INFINITY};
+            float th = fmaxf(fmaxf(w4[0], w4[1]), fmaxf(w4[2], w4[3]));
+            th = fmaxf(th, __shfl_xor_sync(0xffffffffu, th, 1));
+            th = fmaxf(th, __shfl_xor_sync(0xffffffffu, th, 2));
+            const float mn_hi = fmaxf(m_hi, th);
+            const float mu_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
+            alpha_hi = exp2f(m_hi - mu_hi);
+            const float h0 = exp2f(w4[0] - mu_hi), h1 = exp2f(w4[1] - mu_hi), h2 = exp2f(w4[2] - mu_hi),
+                        h3 = exp2f(w4[3] - mu_hi);
+            l_hi = l_hi * alpha_hi + (h0 + h1) + (h2 + h3);
+            m_hi = mn_hi;
+            pa[1] = pack_bf16x2(h0, h1);
+            pa[3] = pack_bf16x2(h2, h3);
+        }
+        // The running maximum rarely moves after the first tiles: skip the 64 multiplies when no row needs them.
+        if (!__all_sync(0xffffffffu, alpha_lo == 1.f && alpha_hi == 1.f)) {
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt) {
+                o[nt][0] *= alpha_lo;
+                o[nt][1] *= alpha_lo;
+                o[nt][2] *= alpha_hi;
+                o[nt][3] *= alpha_hi;
+            }
+        }
+        // ---- O += P V ----
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            const int tok = (mi & 1) * 8 + r;
+#pragma unroll
+            for (int n2 = 0; n2 < 8; ++n2) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, sV_a + sw_tile_off(tok, 2 * n2 + (mi >> 1)));
+                mma_bf16_16816(o[2 * n2], pa, b[0], b[1]);
+                mma_bf16_16816(o[2 * n2 + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncwarp();
+
+        if (pu < u1) {
+            if (lane == 0) issue_tile_sw(p, &tmK, &tmV, pc, wbase + stage * kStageBytes, &bars[stage]);
+            pc.advance(p, nhs);
+            ++pu;
+        }
+        stage = (stage + 1 == NST) ? 0 : stage + 1;
+
+        const bool last_of_seg = (cc.tile + 1 == cc.tiles_b) || (u + 1 == u1);
+        if (last_of_seg) {
+            const int seg = cc.b * nhs + cc.hs;
+            float* out = p.partials + static_cast<size_t>(gw + seg) * (G * kPartialStride);
+            float lt_lo = l_lo, lt_hi = l_hi;
+            lt_lo += __shfl_xor_sync(0xffffffffu, lt_lo, 1);
+            lt_lo += __shfl_xor_sync(0xffffffffu, lt_lo, 2);
+            lt_hi += __shfl_xor_sync(0xffffffffu, lt_hi, 1);
+            lt_hi += __shfl_xor_sync(0xffffffffu, lt_hi, 2);
+            if (r4 < G) {
+                float* og = out + r4 * kPartialStride;
+#pragma unroll
+                for (int nt = 0; nt < 16; ++nt)
+                    *reinterpret_cast<float2*>(og + nt * 8 + 2 * c4) = make_float2(o[nt][0], o[nt][1]);
+                if (c4 == 0) {
+                    og[128] = m_lo;
+                    og[129] = lt_lo;
+                }
+            }
+            if (r4 + 8 < G) {
+                float* og = out + (r4 + 8) * kPartialStride;
+#pragma unroll
+                for (int nt = 0; nt < 16; ++nt)
+                    *reinterpret_cast<float2*>(og + nt * 8 + 2 * c4) = make_float2(o[nt][2], o[nt][3]);
+                if (c4 == 0) {
+                    og[128] = m_hi;
+                    og[129] = lt_hi;
+                }
+            }
+            seg_open = false;
+        }
+        cc.advance(p, nhs);
+    }
+
+    if (failed) {
+        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+        for (int s = 0; s < NST; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
+    }
+}
+
+}  // namespace dkv

@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "dkv_attn.cuh"
+#include "dkv_attn_mma.cuh"
 #include "dkv_extend.cuh"
 #include "dkv_proj.cuh"
 
@@ -112,6 +113,8 @@ struct LayerState {
     void* v_dev = nullptr;
     CUtensorMap tmK_page{}, tmV_page{};  // box rows = min(16, page_size)
     CUtensorMap tmK_16{}, tmV_16{};      // box rows = 16 (contiguous rows)
+    CUtensorMap tmK_sw_page{}, tmV_sw_page{};  // 64 columns x rows_per_box, 128-byte swizzle (mma streaming kernel)
+    CUtensorMap tmK_sw_16{}, tmV_sw_16{};
     CUtensorMap tmK_128{}, tmV_128{};    // 128 rows x 64 columns, 128-byte swizzle (tensor-core extend)
     CUtensorMap tmWk{}, tmWv{};
     int page_shift = 0;
@@ -138,6 +141,7 @@ struct dkv_context {
     int attn_ctas = 0;
     int proj_split_k = 0;
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
+    int attn_mma = -1;                  // -1: tensor-core inner product when 3..16 query heads share a KV head; 0 never; 1 always
     int extend_rowwise = 0;             // 1: extend attends row by row with the decode kernels (reference path for tests)
     // Profiling: kernel launches issued, and CUDA-event pairs around the streaming kernel.
     long long launches = 0;
@@ -305,6 +309,27 @@ cudaError_t attn_dispatch(int variant, int ctas, const CUtensorMap& tmK, const C
     }
 }
 
+template <int NW, int NST>
+cudaError_t attn_mma_launch(int ctas, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, cudaStream_t st) {
+    attn_partial_mma_kernel<NW, NST><<<ctas, NW * 32, attn_smem_bytes<1, NW, NST>(), st>>>(tmK, tmV, p);
+    return cudaGetLastError();
+}
+
+cudaError_t attn_mma_dispatch(int variant, int ctas, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p,
+                              cudaStream_t st) {
+    switch (variant) {
+        case 0: return attn_mma_launch<8, 3>(ctas, tmK, tmV, p, st);
+        case 1: return attn_mma_launch<12, 2>(ctas, tmK, tmV, p, st);
+        default: return attn_mma_launch<16, 1>(ctas, tmK, tmV, p, st);
+    }
+}
+
+template <int NW, int NST>
+cudaError_t attn_mma_set_attr() {
+    return cudaFuncSetAttribute(attn_partial_mma_kernel<NW, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                static_cast<int>(attn_smem_bytes<1, NW, NST>()));
+}
+
 constexpr int kProjStages = 4;
 // stages | control (barriers, TMEM holder) | alignment slack; the epilogue re-uses the stage area for
 // the split-K sum tile (128 x 260 floats) followed by the 64 KB bf16 output staging tile.
@@ -316,7 +341,20 @@ struct ScratchPlan {
     size_t cum, tok_pos, tok_slot, vseq, vrow, partials, kv_new, splitk, q_rot, stage_k, stage_v, total;
 };
 
-int choose_g(int g_total) { return (g_total % 4 == 0) ? 4 : (g_total % 2 == 0) ? 2 : 1; }
+bool use_mma(const dkv_context* ctx, int g_total) {
+    return ctx->attn_mma == 1 || (ctx->attn_mma < 0 && g_total >= 3);
+}
+
+// Query heads that share one pass over a KV head: the mma kernel takes up to 16 rows (the largest divisor of
+// g_total that fits), the CUDA-core kernel 4, 2 or 1.
+int choose_g(const dkv_context* ctx, int g_total) {
+    if (use_mma(ctx, g_total)) {
+        int g = g_total < 16 ? g_total : 16;
+        while (g_total % g != 0) --g;
+        return g;
+    }
+    return (g_total % 4 == 0) ? 4 : (g_total % 2 == 0) ? 2 : 1;
+}
 
 // Variant actually launched for a head grouping (measured on B200, KV in HBM): G == 1: 16 warps x 1 stage
 // (6.5 TB/s); G == 2: 12 warps x 2 stages (6.1 TB/s); G == 4 needs 218 registers per thread and runs 8 warps
@@ -348,7 +386,7 @@ ScratchPlan plan_scratch(const dkv_context* ctx, int64_t rows, int nh_q, int nh_
                          bool with_qrot, size_t stage_bytes = 0) {
     ScratchPlan s{};
     const int g_total = nh_q / nh_kv;
-    const int G = choose_g(g_total);
+    const int G = choose_g(ctx, g_total);
     const int nsub = g_total / G;
     const size_t total_warps = static_cast<size_t>(attn_cta_count(ctx)) * 16;  // upper bound over variants
     size_t off = 0;
@@ -430,6 +468,10 @@ int build_layer(LayerState* L, const dkv_layer_desc* d) {
     if ((rc = encode_pool_map(&L->tmV_page, L->v_dev, d->n_slots, d->nh_kv, L->rows_per_box)) != DKV_OK) return rc;
     if ((rc = encode_pool_map(&L->tmK_16, L->k_dev, d->n_slots, d->nh_kv, kTileTokens)) != DKV_OK) return rc;
     if ((rc = encode_pool_map(&L->tmV_16, L->v_dev, d->n_slots, d->nh_kv, kTileTokens)) != DKV_OK) return rc;
+    if ((rc = encode_tile_map(&L->tmK_sw_page, L->k_dev, d->n_slots, d->nh_kv, 1, L->rows_per_box)) != DKV_OK) return rc;
+    if ((rc = encode_tile_map(&L->tmV_sw_page, L->v_dev, d->n_slots, d->nh_kv, 1, L->rows_per_box)) != DKV_OK) return rc;
+    if ((rc = encode_tile_map(&L->tmK_sw_16, L->k_dev, d->n_slots, d->nh_kv, 1, kTileTokens)) != DKV_OK) return rc;
+    if ((rc = encode_tile_map(&L->tmV_sw_16, L->v_dev, d->n_slots, d->nh_kv, 1, kTileTokens)) != DKV_OK) return rc;
     if ((rc = encode_tile_map(&L->tmK_128, L->k_dev, d->n_slots, d->nh_kv, 1, kExtTile)) != DKV_OK) return rc;
     if ((rc = encode_tile_map(&L->tmV_128, L->v_dev, d->n_slots, d->nh_kv, 1, kExtTile)) != DKV_OK) return rc;
     L->has_weights = (d->wk != nullptr && d->wv != nullptr);
@@ -473,12 +515,14 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
 
 int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool paged, const MergeParams& mp_in,
                      cudaStream_t st, cudaEvent_t join_before_merge = nullptr) {
-    const int G = choose_g(ap.g_total);
+    const int G = choose_g(ctx, ap.g_total);
+    const bool mma = use_mma(ctx, ap.g_total);
     ap.nsub = ap.g_total / G;
     const int ctas = attn_cta_count(ctx);
-    ap.total_warps = ctas * variant_warps(ctx, G);
-    const CUtensorMap& tmK = paged ? L.tmK_page : L.tmK_16;
-    const CUtensorMap& tmV = paged ? L.tmV_page : L.tmV_16;
+    const int mma_variant = ctx->attn_variant < 0 ? 2 : ctx->attn_variant;
+    ap.total_warps = ctas * (mma ? kVarWarps[mma_variant] : variant_warps(ctx, G));
+    const CUtensorMap& tmK = mma ? (paged ? L.tmK_sw_page : L.tmK_sw_16) : (paged ? L.tmK_page : L.tmK_16);
+    const CUtensorMap& tmV = mma ? (paged ? L.tmV_sw_page : L.tmV_sw_16) : (paged ? L.tmV_page : L.tmV_16);
     cudaError_t e;
     std::pair<cudaEvent_t, cudaEvent_t>* ev = nullptr;
     if (ctx->profile_attn) {
@@ -491,7 +535,8 @@ int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool
         if (ctx->attn_events_used < ctx->attn_events.size()) ev = &ctx->attn_events[ctx->attn_events_used++];
     }
     if (ev) DKV_CUDA(cudaEventRecord(ev->first, st));
-    if (G == 4) e = attn_dispatch<4>(effective_variant(ctx, 4), ctas, tmK, tmV, ap, st);
+    if (mma) e = attn_mma_dispatch(mma_variant, ctas, tmK, tmV, ap, st);
+    else if (G == 4) e = attn_dispatch<4>(effective_variant(ctx, 4), ctas, tmK, tmV, ap, st);
     else if (G == 2) e = attn_dispatch<2>(effective_variant(ctx, 2), ctas, tmK, tmV, ap, st);
     else e = attn_dispatch<1>(effective_variant(ctx, 1), ctas, tmK, tmV, ap, st);
     DKV_CUDA(e);
@@ -548,6 +593,9 @@ int dkv_context_create(int device, dkv_context** out) {
     if (e == cudaSuccess) e = attn_set_attr<4, 12, 2>();
     if (e == cudaSuccess) e = attn_set_attr<1, 16, 1>();
     if (e == cudaSuccess) e = attn_set_attr<2, 16, 1>();
+    if (e == cudaSuccess) e = attn_mma_set_attr<8, 3>();
+    if (e == cudaSuccess) e = attn_mma_set_attr<12, 2>();
+    if (e == cudaSuccess) e = attn_mma_set_attr<16, 1>();
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(extend_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kExtSmem + 1024);
     if (e == cudaSuccess)
@@ -595,6 +643,9 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "attn_ctas")) {
         DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
         ctx->attn_ctas = value;
+    } else if (!strcmp(key, "attn_mma")) {
+        DKV_REQUIRE(value >= -1 && value <= 1, "attn_mma must be -1, 0 or 1");
+        ctx->attn_mma = value;
     } else if (!strcmp(key, "extend_rowwise")) {
         ctx->extend_rowwise = value ? 1 : 0;
     } else if (!strcmp(key, "wait_limit_ms")) {

@@ -19,12 +19,13 @@ def _shape(hidden, nh_q, nh_kv, rope=True):
     return workloads.LayerShape(f"t{hidden}-{nh_q}-{nh_kv}", hidden, nh_q, nh_kv, 10000.0 if rope else None)
 
 
-def _run_decode(shape, seq_lens, page_size, cfg_id, kv_on_host=True, mode="project", variant=-1, lid=7):
+def _run_decode(shape, seq_lens, page_size, cfg_id, kv_on_host=True, mode="project", variant=-1, lid=7, mma=-1):
     case = workloads.make_decode_case(shape, seq_lens, page_size, cfg_id, DEV, kv_on_host=kv_on_host)
     k_ref, v_ref = case["k_pool"].cpu().clone(), case["v_pool"].cpu().clone()
     k_before = k_ref.clone()
     ctx = get_context(0)
     ctx.set("attn_variant", variant)
+    ctx.set("attn_mma", mma)
     kernel.register_layer(lid, case["k_pool"], case["v_pool"], case["wk"], case["wv"], case["cos_sin"],
                           page_size=page_size)
     cs_cpu = None if case["cos_sin"] is None else case["cos_sin"].cpu()
@@ -45,6 +46,7 @@ def _run_decode(shape, seq_lens, page_size, cfg_id, kv_on_host=True, mode="proje
     ctx.raise_on_status()
     assert_close(out, ref.view_as(out), "O")
     ctx.set("attn_variant", -1)
+    ctx.set("attn_mma", -1)
     if mode != "none":
         # Stored K/V of the new token: within the reference's write-back threshold; every other slot untouched.
         k_now, v_now = case["k_pool"].cpu(), case["v_pool"].cpu()
@@ -65,6 +67,28 @@ RTOL_KV = 1e-2
 @pytest.mark.parametrize("nh_q,nh_kv", [(4, 4), (8, 2), (6, 3), (7, 7), (8, 1), (12, 2)])
 def test_head_groupings(nh_q, nh_kv):
     _run_decode(_shape(256, nh_q, nh_kv), [1, 2, 17, 40, 129, 300], 16, cfg_id=1)
+
+
+@pytest.mark.parametrize("nh_q,nh_kv,variant", [(16, 1, 0), (16, 1, 2), (32, 1, 1), (9, 3, 2), (5, 1, 0), (28, 2, 1),
+                                                (4, 4, 2), (8, 4, 0)])
+def test_tensor_core_inner_product(nh_q, nh_kv, variant):
+    """The mma form of the streaming kernel: 1..16 query rows per KV head pass (32 -> two passes of 16,
+    28 per 2 -> 14 rows), forced on for the groupings the automatic choice leaves to the CUDA-core form."""
+    _run_decode(_shape(128, nh_q, nh_kv), [1, 2, 16, 17, 40, 129, 300, 1025], 16, cfg_id=11, variant=variant, mma=1)
+
+
+@pytest.mark.parametrize("page_size", [1, 4, 8, 16, 64])
+@pytest.mark.parametrize("host", [True, False])
+def test_tensor_core_inner_product_page_sizes(page_size, host):
+    _run_decode(_shape(128, 8, 2), [1, 5, 16, 31, 64, 65, 200, 333], page_size, cfg_id=12, kv_on_host=host, mma=1)
+
+
+def test_forms_of_the_streaming_kernel_agree():
+    """Same inputs through the CUDA-core and the tensor-core form: outputs differ only by the bf16 rounding of
+    the probabilities."""
+    a = _run_decode(_shape(128, 8, 2), [700, 64, 3, 2048], 16, cfg_id=13, mma=0)
+    b = _run_decode(_shape(128, 8, 2), [700, 64, 3, 2048], 16, cfg_id=13, mma=1)
+    assert (a.float() - b.float()).abs().max().item() < 1e-2
 
 
 @pytest.mark.parametrize("page_size", [1, 2, 4, 8, 16, 32, 64])
