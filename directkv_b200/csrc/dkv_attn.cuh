@@ -432,12 +432,22 @@ struct MergeParams {
     unsigned int* x_count[kMaxExchangeRanks];    // rank p's arrival counters [x_world]
 };
 
-__global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams mp) {
+// WPR warps share one (request, query head) row: each takes blocks of 8 consecutive partial records (loads
+// issued together, one running-maximum update per block) and warp 0 of the row folds the WPR results.  A long
+// single request leaves hundreds of records per row (one per warp of the streaming grid), which a single warp
+// reading them one after the other would turn into the longest kernel of the step.
+constexpr int kMergeThreads = 256;
+constexpr int kMergeBlock = 8;       // records loaded together
+
+template <int WPR>
+__global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const MergeParams mp) {
     const AttnParams& p = mp.a;
-    const int lane = threadIdx.x & 31;
-    const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (wid >= static_cast<long long>(p.batch) * p.nh_q) return;
-    const int b = static_cast<int>(wid / p.nh_q), hq = static_cast<int>(wid % p.nh_q);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int part = warp % WPR, row_in_cta = warp / WPR;
+    const long long wid = static_cast<long long>(blockIdx.x) * (kMergeThreads / 32 / WPR) + row_in_cta;
+    const bool row_valid = wid < static_cast<long long>(p.batch) * p.nh_q;
+    if (WPR == 1 && !row_valid) return;
+    const int b = row_valid ? static_cast<int>(wid / p.nh_q) : 0, hq = row_valid ? static_cast<int>(wid % p.nh_q) : 0;
     const int h = hq / p.g_total, gt = hq % p.g_total;
     const int sub = gt / mp.G, g = gt % mp.G;
     const int nhs = p.nh_kv * p.nsub;
@@ -447,25 +457,70 @@ __global__ void __launch_bounds__(128) attn_merge_kernel(const MergeParams mp) {
     float m = -INFINITY, l = 0.f;
 
     const int tiles_b = p.cum_tiles[b + 1] - p.cum_tiles[b];
-    if (tiles_b > 0) {
+    if (row_valid && tiles_b > 0) {
         const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
         const long long qn = (U + p.total_warps - 1) / p.total_warps;
         const long long s0 = static_cast<long long>(p.cum_tiles[b]) * nhs + static_cast<long long>(hs) * tiles_b;
         const long long e0 = s0 + tiles_b;
         const int seg = b * nhs + hs;
         const int gw_first = static_cast<int>(s0 / qn), gw_last = static_cast<int>((e0 - 1) / qn);
-        for (int gw = gw_first; gw <= gw_last; ++gw) {
-            const float* rec = p.partials + static_cast<size_t>(gw + seg) * (mp.G * kPartialStride) + g * kPartialStride;
-            const float mi = rec[128], li = rec[129];
-            const float4 oi = *reinterpret_cast<const float4*>(rec + 4 * lane);
-            const float mn = fmaxf(m, mi);
+        const int n = gw_last - gw_first + 1;
+        const float* rec0 = p.partials + static_cast<size_t>(gw_first + seg) * (mp.G * kPartialStride) + g * kPartialStride;
+        const size_t rec_stride = static_cast<size_t>(mp.G) * kPartialStride;
+        for (int base = part * kMergeBlock; base < n; base += WPR * kMergeBlock) {
+            float mi[kMergeBlock], li[kMergeBlock];
+            float4 oi[kMergeBlock];
+#pragma unroll
+            for (int j = 0; j < kMergeBlock; ++j) {
+                const bool on = base + j < n;
+                const float* rec = rec0 + static_cast<size_t>(on ? base + j : base) * rec_stride;
+                const float2 ml = *reinterpret_cast<const float2*>(rec + 128);
+                oi[j] = *reinterpret_cast<const float4*>(rec + 4 * lane);
+                mi[j] = on ? ml.x : -INFINITY;
+                li[j] = on ? ml.y : 0.f;
+            }
+            float mn = m;
+#pragma unroll
+            for (int j = 0; j < kMergeBlock; ++j) mn = fmaxf(mn, mi[j]);
             const float mu = (mn == -INFINITY) ? 0.f : mn;
-            const float a = exp2f(m - mu), c = exp2f(mi - mu);
-            acc.x = acc.x * a + oi.x * c;
-            acc.y = acc.y * a + oi.y * c;
-            acc.z = acc.z * a + oi.z * c;
-            acc.w = acc.w * a + oi.w * c;
-            l = l * a + li * c;
+            const float a = exp2f(m - mu);
+            acc.x *= a;
+            acc.y *= a;
+            acc.z *= a;
+            acc.w *= a;
+            l *= a;
+#pragma unroll
+            for (int j = 0; j < kMergeBlock; ++j) {
+                const float c = exp2f(mi[j] - mu);
+                acc.x += oi[j].x * c;
+                acc.y += oi[j].y * c;
+                acc.z += oi[j].z * c;
+                acc.w += oi[j].w * c;
+                l += li[j] * c;
+            }
+            m = mn;
+        }
+    }
+
+    if (WPR > 1) {
+        __shared__ float4 s_acc[kMergeThreads / 32][32];
+        __shared__ float2 s_ml[kMergeThreads / 32];
+        s_acc[warp][lane] = acc;
+        if (lane == 0) s_ml[warp] = make_float2(m, l);
+        __syncthreads();
+        if (part != 0 || !row_valid) return;
+#pragma unroll
+        for (int j = 1; j < WPR; ++j) {
+            const float2 ml = s_ml[warp + j];
+            const float4 oj = s_acc[warp + j][lane];
+            const float mn = fmaxf(m, ml.x);
+            const float mu = (mn == -INFINITY) ? 0.f : mn;
+            const float a = exp2f(m - mu), c = exp2f(ml.x - mu);
+            acc.x = acc.x * a + oj.x * c;
+            acc.y = acc.y * a + oj.y * c;
+            acc.z = acc.z * a + oj.z * c;
+            acc.w = acc.w * a + oj.w * c;
+            l = l * a + ml.y * c;
             m = mn;
         }
     }

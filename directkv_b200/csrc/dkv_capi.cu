@@ -15,6 +15,7 @@
 
 #include "dkv_attn.cuh"
 #include "dkv_attn_mma.cuh"
+#include "dkv_proj_decode.cuh"
 #include "dkv_extend.cuh"
 #include "dkv_proj.cuh"
 
@@ -77,12 +78,12 @@ int encode_pool_map(CUtensorMap* m, void* base, int64_t n_slots, int nh, int row
 }
 
 // Row-major [rows, cols] bf16 matrix as a 2-D map; box = 128 rows x 64 columns, 128-byte swizzle.
-int encode_operand_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols) {
+int encode_operand_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int box_rows = 128) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) return fail(DKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t gstr[1] = {(cuuint64_t)cols * 2};
-    cuuint32_t box[2] = {64, 128};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstr, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -141,6 +142,7 @@ struct dkv_context {
     int attn_ctas = 0;
     int proj_split_k = 0;
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
+    int proj_decode = -1;               // -1: swapped-operand projection kernel when T <= 128; 0 never; 1 same as -1
     int attn_mma = -1;                  // -1: tensor-core inner product when 3..16 query heads share a KV head; 0 never; 1 always
     int extend_rowwise = 0;             // 1: extend attends row by row with the decode kernels (reference path for tests)
     // Profiling: kernel launches issued, and CUDA-event pairs around the streaming kernel.
@@ -382,6 +384,20 @@ void proj_split(const dkv_context* ctx, int T, int nh_kv, int H, int* split_k, i
     *split_k = (nchunks + c - 1) / c;  // no empty slice
 }
 
+// Split of the hidden dimension for the decode-batch projection: one CTA per (KV head, slice), about one
+// CTA per SM, at least four 64-column chunks per slice.
+void proj_decode_split(const dkv_context* ctx, int nh_kv, int H, int* split_k, int* cps) {
+    const int nchunks = H / kProjBK;
+    int s = ctx->proj_split_k > 0 ? ctx->proj_split_k : ctx->sm_count / (nh_kv > 0 ? nh_kv : 1);
+    if (ctx->proj_split_k <= 0 && s > nchunks / 4) s = nchunks / 4;
+    if (s < 1) s = 1;
+    if (s > nchunks) s = nchunks;
+    if (nh_kv > kMaxCounters) s = 1;
+    const int c = (nchunks + s - 1) / s;
+    *cps = c;
+    *split_k = (nchunks + c - 1) / c;
+}
+
 ScratchPlan plan_scratch(const dkv_context* ctx, int64_t rows, int nh_q, int nh_kv, int hidden, bool with_proj,
                          bool with_qrot, size_t stage_bytes = 0) {
     ScratchPlan s{};
@@ -401,10 +417,20 @@ ScratchPlan plan_scratch(const dkv_context* ctx, int64_t rows, int nh_q, int nh_
     if (with_proj && hidden > 0) {
         int split_k, cps;
         proj_split(ctx, static_cast<int>(rows), nh_kv, hidden, &split_k, &cps);
+        size_t bytes = 0;
         if (split_k > 1) {
             const size_t tiles = static_cast<size_t>((rows + kProjBM - 1) / kProjBM) * nh_kv;
-            off += align256(static_cast<size_t>(split_k) * tiles * kProjBM * kProjBN * 4);
+            bytes = static_cast<size_t>(split_k) * tiles * kProjBM * kProjBN * 4;
         }
+        // The decode-batch kernel (up to 128 rows) splits differently; a plan made for many rows also covers
+        // a later call with few.
+        proj_decode_split(ctx, nh_kv, hidden, &split_k, &cps);
+        if (split_k > 1) {
+            const size_t n_pad = pd_padded_tokens(static_cast<int>(rows < kPdMaxTokens ? rows : kPdMaxTokens));
+            const size_t dec = static_cast<size_t>(split_k) * nh_kv * 2 * n_pad * kProjHead * 4;
+            bytes = bytes > dec ? bytes : dec;
+        }
+        off += align256(bytes);
     }
     s.q_rot = off;
     if (with_qrot) off += align256(static_cast<size_t>(rows) * nh_q * 128 * 2);
@@ -487,14 +513,16 @@ int build_layer(LayerState* L, const dkv_layer_desc* d) {
 // Projection of T rows of X with RoPE and write-back (tcgen05 kernel).
 int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int T, const int* tok_pos,
                       const int* tok_slot, bool store_pool, __nv_bfloat16* kv_new, float* splitk, cudaStream_t st) {
+    const bool small = T <= kPdMaxTokens && ctx->proj_decode != 0;
     CUtensorMap tmX;
-    int rc = encode_operand_map(&tmX, x, T, L.d.hidden);
+    int rc = encode_operand_map(&tmX, x, T, L.d.hidden, small ? pd_padded_tokens(T) : 128);
     if (rc != DKV_OK) return rc;
     ProjParams pp{};
     pp.T = T;
     pp.H = L.d.hidden;
     pp.nh_kv = L.d.nh_kv;
-    proj_split(ctx, T, L.d.nh_kv, L.d.hidden, &pp.split_k, &pp.chunks_per_split);
+    if (small) proj_decode_split(ctx, L.d.nh_kv, L.d.hidden, &pp.split_k, &pp.chunks_per_split);
+    else proj_split(ctx, T, L.d.nh_kv, L.d.hidden, &pp.split_k, &pp.chunks_per_split);
     pp.tok_pos = tok_pos;
     pp.tok_slot = tok_slot;
     pp.cos_sin = L.d.cos_sin;
@@ -506,8 +534,13 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
     pp.splitk_scratch = splitk;
     pp.tile_counters = ctx->counters;
     pp.status = ctx->status;
-    dim3 grid(L.d.nh_kv, (T + kProjBM - 1) / kProjBM, pp.split_k);
-    proj_rope_kernel<kProjStages><<<grid, 128, kProjSmem, st>>>(tmX, L.tmWk, L.tmWv, pp);
+    if (small) {
+        dim3 grid(L.d.nh_kv, pp.split_k);
+        proj_rope_decode_kernel<<<grid, 128, pd_smem_bytes(pd_padded_tokens(T)), st>>>(tmX, L.tmWk, L.tmWv, pp);
+    } else {
+        dim3 grid(L.d.nh_kv, (T + kProjBM - 1) / kProjBM, pp.split_k);
+        proj_rope_kernel<kProjStages><<<grid, 128, kProjSmem, st>>>(tmX, L.tmWk, L.tmWv, pp);
+    }
     DKV_CUDA(cudaGetLastError());
     ctx->launches += 1;
     return DKV_OK;
@@ -546,9 +579,12 @@ int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool
     MergeParams mp = mp_in;
     mp.a = ap;
     mp.G = G;
-    const long long warps = static_cast<long long>(ap.batch) * ap.nh_q;
-    const int blocks = static_cast<int>((warps + 3) / 4);
-    attn_merge_kernel<<<blocks, 128, 0, st>>>(mp);
+    // Records per row are about (warps of the streaming grid) / (request x head-slot segments) + 2: with few
+    // segments eight warps share a row.
+    const long long rows = static_cast<long long>(ap.batch) * ap.nh_q;
+    const long long segments = static_cast<long long>(ap.batch) * ap.nh_kv * ap.nsub;
+    if (segments * 8 < ap.total_warps) attn_merge_kernel<8><<<static_cast<int>(rows), kMergeThreads, 0, st>>>(mp);
+    else attn_merge_kernel<1><<<static_cast<int>((rows + 7) / 8), kMergeThreads, 0, st>>>(mp);
     DKV_CUDA(cudaGetLastError());
     return DKV_OK;
 }
@@ -601,6 +637,9 @@ int dkv_context_create(int device, dkv_context** out) {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(proj_rope_kernel<kProjStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kProjSmem));
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(proj_rope_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(pd_smem_bytes(kPdMaxTokens)));
     if (e != cudaSuccess) {
         delete ctx;
         return fail(DKV_ERR_CUDA, "context set-up failed: %s", cudaGetErrorString(e));
@@ -643,6 +682,9 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "attn_ctas")) {
         DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
         ctx->attn_ctas = value;
+    } else if (!strcmp(key, "proj_decode")) {
+        DKV_REQUIRE(value >= -1 && value <= 1, "proj_decode must be -1, 0 or 1");
+        ctx->proj_decode = value;
     } else if (!strcmp(key, "attn_mma")) {
         DKV_REQUIRE(value >= -1 && value <= 1, "attn_mma must be -1, 0 or 1");
         ctx->attn_mma = value;

@@ -254,7 +254,10 @@ extern "C" int dkv_decode_noalloc(const dkv_noalloc_args* a, void* stream) {
     mp.lse = a->lse_out;
     mp.part_out = nullptr;
     const long long rows = static_cast<long long>(a->batch) * a->nh_q;
-    attn_merge_kernel<<<static_cast<int>((rows + 3) / 4), 128, 0, st>>>(mp);
+    if (static_cast<long long>(a->batch) * a->nh_kv * nsub * 8 < ap.total_warps)
+        attn_merge_kernel<8><<<static_cast<int>(rows), kMergeThreads, 0, st>>>(mp);
+    else
+        attn_merge_kernel<1><<<static_cast<int>((rows + 7) / 8), kMergeThreads, 0, st>>>(mp);
     NA_CUDA(cudaGetLastError());
 
     if (a->sync_and_check) {

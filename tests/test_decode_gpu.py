@@ -91,6 +91,32 @@ def test_forms_of_the_streaming_kernel_agree():
     assert (a.float() - b.float()).abs().max().item() < 1e-2
 
 
+@pytest.mark.parametrize("batch", [1, 15, 16, 17, 33, 64, 65, 128, 129])
+@pytest.mark.parametrize("hidden", [64, 320, 4096])
+def test_projection_batch_sizes(batch, hidden):
+    """Decode batches on both projection kernels: up to 128 tokens the swapped-operand kernel (tokens on the
+    N side, 16..128 padded columns, split-K by KV head), above that the 128-token-tile kernel."""
+    lens = [1 + (7 * i) % 40 for i in range(batch)]
+    _run_decode(_shape(hidden, 4, 2), lens, 16, cfg_id=20 + batch)
+
+
+def test_projection_kernels_agree():
+    ctx = get_context(0)
+    outs = []
+    for flag in (0, -1):
+        ctx.set("proj_decode", flag)
+        outs.append(_run_decode(_shape(1024, 8, 4), [30, 1, 17, 64, 5], 16, cfg_id=77))
+    ctx.set("proj_decode", -1)
+    assert (outs[0].float() - outs[1].float()).abs().max().item() < 1e-2
+
+
+def test_long_single_request_merge():
+    """One long request: every warp of the streaming grid leaves a partial record for the same few rows, which
+    the merge kernel folds with eight warps per row."""
+    _run_decode(_shape(128, 8, 2), [40000], 16, cfg_id=30, kv_on_host=False)
+    _run_decode(_shape(128, 2, 2), [25000, 3], 16, cfg_id=31, kv_on_host=False, mma=0)
+
+
 @pytest.mark.parametrize("page_size", [1, 2, 4, 8, 16, 32, 64])
 def test_page_sizes(page_size):
     _run_decode(_shape(128, 4, 2), [1, 5, 16, 31, 64, 65, 200, 333], page_size, cfg_id=2)
