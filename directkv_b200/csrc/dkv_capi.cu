@@ -16,6 +16,7 @@
 #include "dkv_attn.cuh"
 #include "dkv_attn_mma.cuh"
 #include "dkv_proj_decode.cuh"
+#include "dkv_extend_pp.cuh"
 #include "dkv_extend.cuh"
 #include "dkv_proj.cuh"
 
@@ -144,6 +145,7 @@ struct dkv_context {
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
     int proj_decode = -1;               // -1: swapped-operand projection kernel when T <= 128; 0 never; 1 same as -1
     int attn_mma = -1;                  // -1: tensor-core inner product when 3..16 query heads share a KV head; 0 never; 1 always
+    int extend_pingpong = 1;            // two query tiles per CTA with specialised warps (0: one tile, four warps)
     int extend_rowwise = 0;             // 1: extend attends row by row with the decode kernels (reference path for tests)
     // Profiling: kernel launches issued, and CUDA-event pairs around the streaming kernel.
     long long launches = 0;
@@ -635,6 +637,8 @@ int dkv_context_create(int device, dkv_context** out) {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(extend_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kExtSmem + 1024);
     if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(extend_attn_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPpSmem);
+    if (e == cudaSuccess)
         e = cudaFuncSetAttribute(proj_rope_kernel<kProjStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kProjSmem));
     if (e == cudaSuccess)
@@ -688,6 +692,8 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "attn_mma")) {
         DKV_REQUIRE(value >= -1 && value <= 1, "attn_mma must be -1, 0 or 1");
         ctx->attn_mma = value;
+    } else if (!strcmp(key, "extend_pingpong")) {
+        ctx->extend_pingpong = value != 0;
     } else if (!strcmp(key, "extend_rowwise")) {
         ctx->extend_rowwise = value ? 1 : 0;
     } else if (!strcmp(key, "wait_limit_ms")) {
@@ -1081,8 +1087,13 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         ep.scale_log2 = scale * 1.4426950408889634f;
         ep.out = static_cast<__nv_bfloat16*>(O);
         ep.status = ctx->status;
-        dim3 grid((S_new + TQ - 1) / TQ, nh_kv * nsub, B);
-        extend_attn_kernel<<<grid, 128, kExtSmem + 1024, st>>>(tmQ, *tmK, *tmV, ep);
+        if (ctx->extend_pingpong != 0) {
+            dim3 grid((S_new + 2 * TQ - 1) / (2 * TQ), nh_kv * nsub, B);
+            extend_attn_pp_kernel<<<grid, kPpThreads, kPpSmem, st>>>(tmQ, *tmK, *tmV, ep);
+        } else {
+            dim3 grid((S_new + TQ - 1) / TQ, nh_kv * nsub, B);
+            extend_attn_kernel<<<grid, 128, kExtSmem + 1024, st>>>(tmQ, *tmK, *tmV, ep);
+        }
         DKV_CUDA(cudaGetLastError());
         ctx->launches += 1;
         return DKV_OK;

@@ -161,6 +161,33 @@ def test_tensor_core_extend_shapes(nh_q, nh_kv, S_new, S_past, host):
     _run_fwd(X, Wk, Wv, Q, K, V, cs, True, S_past, kv_on_host=host)
 
 
+@pytest.mark.parametrize("causal", [True, False])
+def test_extend_kernel_forms_agree(causal):
+    """Two query tiles per CTA with specialised warps (O kept in TMEM, lazily rescaled) against the one-tile form."""
+    ctx = get_context(0)
+    X, Wk, Wv, Q, K, V, cs = _rand_case(2, 8, 2, 700, 300, 128, seed=41)
+    outs = []
+    for pp in (1, 0):
+        ctx.set("extend_pingpong", pp)
+        Kd, Vd = K.clone().to(DEV), V.clone().to(DEV)
+        outs.append(kernel.smpv2_fwd(X.to(DEV), Wk.to(DEV), Wv.to(DEV), Q.to(DEV), Kd, Vd, cs.to(DEV), SCALE, causal,
+                                     300, -1).float().cpu())
+    ctx.set("extend_pingpong", 1)
+    ctx.raise_on_status()
+    assert (outs[0] - outs[1]).abs().max() < 2e-2
+
+
+def test_extend_large_scores_rescale():
+    """Scores that keep growing along the keys force the lazy rescale of O (steps of more than 2^8) many times."""
+    B, nh, S_new, S_past, H = 1, 4, 512, 0, 128
+    X, Wk, Wv, Q, K, V, cs = _rand_case(B, nh, nh, S_new, S_past, H, seed=43, rope=False)
+    ramp = torch.linspace(0.2, 6.0, S_new).view(1, S_new, 1)
+    X = (X.float() * ramp).to(torch.bfloat16)
+    Q = (Q.float() * 3.0).to(torch.bfloat16)
+    Wk = (Wk.float() * 8.0).to(torch.bfloat16)
+    _run_fwd(X, Wk, Wv, Q, K, V, cs, True, S_past, kv_on_host=False)
+
+
 def test_extend_paths_agree():
     """The tensor-core extend kernel and the row-streamed path (decode kernels, one virtual request per new
     row) implement the same function: compare them directly, non-causal included."""
