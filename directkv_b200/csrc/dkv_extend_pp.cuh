@@ -213,40 +213,73 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const int col0 = j * kExtTile;
             // Warp-uniform: only tiles on the diagonal (or holding the end of the request) need the comparison.
             const bool masked = (col0 + kExtTile - 1 > first_limit) || !(p.scale_log2 > 0.f);
-            // ---- pass 1: row maximum of the visible scores ----
-            float m_new = m_used;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t r0[32], r1[32];
-                tmem_ld_32x32(tS + c * 64, r0);
-                tmem_ld_32x32(tS + c * 64 + 32, r1);
-                tmem_ld_wait();
-                if (masked) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (col0 + c * 64 + i <= my_limit) m_new = fmaxf(m_new, __uint_as_float(r0[i]) * p.scale_log2);
-                        if (col0 + c * 64 + 32 + i <= my_limit) m_new = fmaxf(m_new, __uint_as_float(r1[i]) * p.scale_log2);
-                    }
-                } else {
-                    float a = -INFINITY, bmax = -INFINITY;
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        a = fmaxf(a, __uint_as_float(r0[i]));
-                        bmax = fmaxf(bmax, __uint_as_float(r1[i]));
-                    }
-                    m_new = fmaxf(m_new, fmaxf(a, bmax) * p.scale_log2);   // scale_log2 > 0
-                }
-            }
             // The previous P V of this tile must be done before P is overwritten or O is touched.
             if (j > 0) {
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_o[g], (j - 1) & 1) && !ctl->abort);
                 if (!ok) break;
                 tc_fence_after_sync();
             }
-            // ---- move the maximum only when it grew by more than the step (warp-uniform decision) ----
-            const bool grow = (m_new > m_used + kPpRescaleStep) || (m_used == -INFINITY);
-            if (__any_sync(0xffffffffu, grow)) {
-                const float m_to = (m_new == -INFINITY) ? 0.f : m_new;
+            // One pass over S in the common case: probabilities are formed against the maximum in use while
+            // the tile's own maximum is tracked; only when that one is more than the step above (or on the
+            // first tile) is the maximum moved, O and l rescaled, and the pass repeated.
+            float psum = 0.f, m_tile = -INFINITY;
+            auto sweep = [&](const float neg_m, const bool track) {
+                psum = 0.f;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tS + c * 32, r);
+                    tmem_ld_wait();
+                    float pv[32];
+                    if (masked) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const bool vis = col0 + c * 32 + i <= my_limit;
+                            const float sc = __uint_as_float(r[i]) * p.scale_log2;
+                            if (track && vis) m_tile = fmaxf(m_tile, sc);
+                            pv[i] = vis ? ex2_approx(sc + neg_m) : 0.f;
+                            psum += pv[i];
+                        }
+                    } else {
+                        float raw = -INFINITY;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (track) raw = fmaxf(raw, __uint_as_float(r[i]));
+                            pv[i] = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+                            psum += pv[i];
+                        }
+                        if (track) m_tile = fmaxf(m_tile, raw * p.scale_log2);   // scale_log2 > 0 on this path
+                    }
+#pragma unroll
+                    for (int q8 = 0; q8 < 4; ++q8) {
+                        uint4 w;
+                        w.x = pack_bf16x2(pv[q8 * 8 + 0], pv[q8 * 8 + 1]);
+                        w.y = pack_bf16x2(pv[q8 * 8 + 2], pv[q8 * 8 + 3]);
+                        w.z = pack_bf16x2(pv[q8 * 8 + 4], pv[q8 * 8 + 5]);
+                        w.w = pack_bf16x2(pv[q8 * 8 + 6], pv[q8 * 8 + 7]);
+                        const int c8 = c * 4 + q8;             // 16-byte chunk within the 128-key row
+                        *reinterpret_cast<uint4*>(sPg + (c8 >> 3) * kExtHalfBytes + row * 128 + (((c8 & 7) ^ (row & 7)) << 4)) = w;
+                    }
+                }
+            };
+            if (j == 0) {
+                // No maximum yet: a tracking-only sweep would waste the exponentials, so find the maximum first.
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tS + c * 32, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (!masked || col0 + c * 32 + i <= my_limit) m_tile = fmaxf(m_tile, __uint_as_float(r[i]) * p.scale_log2);
+                }
+            } else {
+                sweep(-m_used, true);
+            }
+            const bool grow = (m_tile > m_used + kPpRescaleStep) || (m_used == -INFINITY);
+            if (__any_sync(0xffffffffu, grow)) {                      // warp-uniform
+                float m_to = fmaxf(m_used, m_tile);
+                if (m_to == -INFINITY) m_to = 0.f;
                 const float alpha = exp2f(m_used - m_to);             // 0 on the first tile
                 l *= alpha;
                 m_used = m_to;
@@ -262,32 +295,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     }
                     tmem_st_wait();
                 }
-            }
-            // ---- pass 2: probabilities -> bf16 -> smem (K-major, swizzled like a TMA tile) ----
-            const float neg_m = -m_used;
-            float psum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tS + c * 32, r);
-                tmem_ld_wait();
-                float pv[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float e = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-                    pv[i] = (!masked || col0 + c * 32 + i <= my_limit) ? e : 0.f;
-                    psum += pv[i];
-                }
-#pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {
-                    uint4 w;
-                    w.x = pack_bf16x2(pv[q8 * 8 + 0], pv[q8 * 8 + 1]);
-                    w.y = pack_bf16x2(pv[q8 * 8 + 2], pv[q8 * 8 + 3]);
-                    w.z = pack_bf16x2(pv[q8 * 8 + 4], pv[q8 * 8 + 5]);
-                    w.w = pack_bf16x2(pv[q8 * 8 + 6], pv[q8 * 8 + 7]);
-                    const int c8 = c * 4 + q8;                 // 16-byte chunk within the 128-key row
-                    *reinterpret_cast<uint4*>(sPg + (c8 >> 3) * kExtHalfBytes + row * 128 + (((c8 & 7) ^ (row & 7)) << 4)) = w;
-                }
+                sweep(-m_used, false);
             }
             l += psum;
             // Rows of the last tile past the request's last token may hold anything: V must be finite there
