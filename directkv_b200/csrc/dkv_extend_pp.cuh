@@ -11,30 +11,36 @@
 //   warps 4-7   softmax of tile 0 (thread = query row = TMEM lane)
 //   warps 8-11  softmax of tile 1
 //
-// While one group exponentiates, the tensor core works for the other.  O stays in TMEM: the P V product
-// accumulates into it, and a row's running maximum is only moved (O and l rescaled through tcgen05.ld/st)
-// when it grew by more than 2^8, so most tiles never touch O outside the tensor core.  Probabilities are
-// therefore at most 256; sums stay fp32 and the final O / l is exact in the same sense as before.
+// The keys of a 128-row K/V tile are processed as two half-tiles of 64, each with its own S buffer in TMEM
+// in TMEM, so the issuer runs two half-tiles ahead of a group's softmax
+// (S(t+2) is being multiplied while S(t) is exponentiated) and P V(t) overlaps the sweep of t+1; the two
+// groups fill each other's gaps.  P never touches shared memory: the bf16 probabilities are stored back
+// over the S buffer they came from (two per 32-bit column) and the second product reads its A operand
+// from tensor memory, which leaves room for a five-slot K/V ring.  O stays in TMEM: the P V product accumulates into it, and a row's
+// reference maximum is only moved (O and l rescaled through tcgen05.ld/st) when the true maximum grew by
+// more than 2^8, so most half-tiles never touch O outside the tensor core.  Probabilities are therefore at
+// most 256; sums stay fp32 and the final O / l is exact in the same sense as before.
 //
-// TMEM columns: S_0 [0,128)  S_1 [128,256)  O_0 [256,384)  O_1 [384,512).
+// TMEM columns: S_0 [0,64) [64,128)   S_1 [128,192) [192,256)   O_0 [256,384)   O_1 [384,512).
 #pragma once
 
 #include "dkv_extend.cuh"
 
 namespace dkv {
 
-constexpr int kPpSlots = 3;                                   // ring of [128 x 128] bf16 tiles: K and V alternate
+constexpr int kPpSlots = 5;                                   // ring of [128 x 128] bf16 tiles: K and V alternate
 constexpr int kPpThreads = 384;
-constexpr int kPpSmem = 2 * kExtTileBytes /*Q0,Q1*/ + 2 * kExtTileBytes /*P0,P1*/ + kPpSlots * kExtTileBytes + 256 + 1024;
+constexpr int kPpSmem = 2 * kExtTileBytes /*Q0,Q1*/ + kPpSlots * kExtTileBytes + 256 + 1024;
 constexpr float kPpRescaleStep = 8.f;                         // log2 units the maximum may lag behind
+constexpr int kPpHalf = 64;                                   // keys per half-tile
 
 struct PpCtrl {
     uint64_t bar_q;
     uint64_t full[kPpSlots];
     uint64_t empty[kPpSlots];
-    uint64_t bar_s[2];        // S_g(j) complete
-    uint64_t bar_p[2];        // P_g(j) stored, S_g consumed, O_g rescaled: 128 arrivals
-    uint64_t bar_o[2];        // O_g += P_g V(j) complete
+    uint64_t bar_s[2][2];     // [g][buf] S_g(t) complete, buf = t & 1
+    uint64_t bar_p[2][2];     // [g][buf] P_g(t) stored, S buffer consumed, O_g rescaled: 128 arrivals
+    uint64_t bar_o[2][2];     // [g][buf] O_g += P_g(t) V complete
     uint32_t tmem;
     volatile int abort;
 };
@@ -45,8 +51,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sQ = smem;                                       // tile g at + g * 32 KB
-    uint8_t* sP = sQ + 2 * kExtTileBytes;
-    uint8_t* sRing = sP + 2 * kExtTileBytes;
+    uint8_t* sRing = sQ + 2 * kExtTileBytes;
     PpCtrl* ctl = reinterpret_cast<PpCtrl*>(sRing + kPpSlots * kExtTileBytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -59,14 +64,14 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int q0 = qt * 2 * TQ;                               // first new token of tile 0; tile 1 starts at q0 + TQ
     const int row_slot0 = static_cast<int>(static_cast<long long>(p.vrow ? p.vrow[b] : b) * p.row_stride);
     const int s_total = past + p.S_new;
-    int n_tiles[2];
+    int n_half[2];                                            // half-tiles of 64 keys each group walks
 #pragma unroll
     for (int g = 0; g < 2; ++g) {
         int kv_end = p.is_causal ? past + q0 + (g + 1) * TQ : s_total;
         if (kv_end > s_total) kv_end = s_total;
-        n_tiles[g] = (kv_end + kExtTile - 1) / kExtTile;      // n_tiles[1] >= n_tiles[0] >= 1
+        n_half[g] = (kv_end + kPpHalf - 1) / kPpHalf;         // n_half[1] >= n_half[0] >= 1
     }
-    const int n_max = n_tiles[1];
+    const int n_max = (n_half[1] + 1) >> 1;                   // K/V tiles to load
 
     if (tid == 0) {
         mbar_init(&ctl->bar_q, 1);
@@ -74,11 +79,12 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
-        for (int g = 0; g < 2; ++g) {
-            mbar_init(&ctl->bar_s[g], 1);
-            mbar_init(&ctl->bar_p[g], 128);
-            mbar_init(&ctl->bar_o[g], 1);
-        }
+        for (int g = 0; g < 2; ++g)
+            for (int bf = 0; bf < 2; ++bf) {
+                mbar_init(&ctl->bar_s[g][bf], 1);
+                mbar_init(&ctl->bar_p[g][bf], 128);
+                mbar_init(&ctl->bar_o[g][bf], 1);
+            }
         ctl->abort = 0;
         fence_mbar_init();
         fence_proxy_async_smem();
@@ -125,7 +131,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer ------------------------------------------------
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(kExtTile, kExtTile);
+            constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(kExtTile, kPpHalf);
             constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(kExtTile, kExtTile) | (1u << 16);   // B (V) is MN-major
             bool ok = mbar_wait_bounded(&ctl->bar_q, 0);
             int ring_ready = -1;                              // highest ring sequence number known to have landed
@@ -135,52 +141,49 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     ok = mbar_wait_bounded(&ctl->full[nq % kPpSlots], (nq / kPpSlots) & 1);
                     ring_ready = nq;
                 }
+                tc_fence_after_sync();
             };
-            auto issue_qk = [&](int g, int j) {               // S_g = Q_g K(j)^T
-                const uint32_t qa = smem_u32(sQ + g * kExtTileBytes), ka = smem_u32(sRing + ((2 * j) % kPpSlots) * kExtTileBytes);
+            const int last1 = n_half[1] - 1;
+            auto issue_qk = [&](int g, int t) {               // S_g[t & 1] = Q_g K(rows 64 (t & 1) ... of tile t >> 1)^T
+                const int q = 2 * (t >> 1);
+                wait_ring(q);
+                if (!ok) return;
+                const uint32_t qa = smem_u32(sQ + g * kExtTileBytes);
+                const uint32_t ka = smem_u32(sRing + (q % kPpSlots) * kExtTileBytes) + (t & 1) * kPpHalf * 128;
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const uint32_t off = (k >> 2) * kExtHalfBytes + (k & 3) * 32;
-                    umma_bf16_ss(tmem_base + g * 128, umma_desc_k_sw128(qa + off), umma_desc_k_sw128(ka + off), idesc_qk,
-                                 k > 0 ? 1u : 0u);
+                    umma_bf16_ss(tmem_base + g * 128 + (t & 1) * kPpHalf, umma_desc_k_sw128(qa + off),
+                                 umma_desc_k_sw128(ka + off), idesc_qk, k > 0 ? 1u : 0u);
                 }
-                umma_commit(&ctl->bar_s[g]);
-                if (g == 1) umma_commit(&ctl->empty[(2 * j) % kPpSlots]);       // tile 1 is the last reader of K(j)
+                umma_commit(&ctl->bar_s[g][t & 1]);
+                // Tile 1 issues last: its second half (or its very last half-tile) is the last reader of K(t >> 1).
+                if (g == 1 && ((t & 1) || t == last1)) umma_commit(&ctl->empty[q % kPpSlots]);
             };
-            auto issue_pv = [&](int g, int j) {               // O_g (+)= P_g V(j)
-                const uint32_t pa = smem_u32(sP + g * kExtTileBytes), va = smem_u32(sRing + ((2 * j + 1) % kPpSlots) * kExtTileBytes);
+            auto issue_pv = [&](int g, int t) {               // O_g (+)= P_g[t & 1] V(rows 64 (t & 1) ... of tile t >> 1)
+                const int q = 2 * (t >> 1) + 1;
+                wait_ring(q);
+                if (!ok) return;
+                const uint32_t pa = tmem_base + g * 128 + (t & 1) * kPpHalf;      // P lies over the S buffer it came from
+                const uint32_t va = smem_u32(sRing + (q % kPpSlots) * kExtTileBytes) + (t & 1) * kPpHalf * 128;
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const uint32_t aoff = (k >> 2) * kExtHalfBytes + (k & 3) * 32;   // 16 keys along K of P
-                    const uint32_t boff = k * 16 * 128;                               // 16 key rows of V
-                    umma_bf16_ss(tmem_base + 256 + g * 128, umma_desc_k_sw128(pa + aoff),
-                                 umma_desc_mn_sw128(va + boff, kExtHalfBytes), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
-                }
-                umma_commit(&ctl->bar_o[g]);
-                if (g == 1) umma_commit(&ctl->empty[(2 * j + 1) % kPpSlots]);
+                for (int k = 0; k < 4; ++k)                   // 16 keys per step = 8 packed columns of P
+                    umma_bf16_ts(tmem_base + 256 + g * 128, pa + k * 8, umma_desc_mn_sw128(va + k * 16 * 128, kExtHalfBytes),
+                                 idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&ctl->bar_o[g][t & 1]);
+                if (g == 1 && ((t & 1) || t == last1)) umma_commit(&ctl->empty[q % kPpSlots]);
             };
-            wait_ring(0);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_qk(0, 0);
-                issue_qk(1, 0);
-            }
-            for (int j = 0; ok && j < n_max; ++j) {
+            for (int t = 0; ok && t < 2; ++t)
+                for (int g = 0; ok && g < 2; ++g)
+                    if (t < n_half[g]) issue_qk(g, t);
+            for (int t = 0; ok && t < n_half[1]; ++t) {
                 for (int g = 0; ok && g < 2; ++g) {
-                    if (j >= n_tiles[g]) continue;
-                    ok = mbar_wait_bounded(&ctl->bar_p[g], j & 1) && !ctl->abort;
+                    if (t >= n_half[g]) continue;
+                    ok = mbar_wait_bounded(&ctl->bar_p[g][t & 1], (t >> 1) & 1) && !ctl->abort;
                     if (!ok) break;
                     tc_fence_after_sync();
-                    if (j + 1 < n_tiles[g]) {
-                        wait_ring(2 * (j + 1));
-                        if (!ok) break;
-                        tc_fence_after_sync();
-                        issue_qk(g, j + 1);
-                    }
-                    wait_ring(2 * j + 1);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_pv(g, j);
+                    issue_pv(g, t);                             // reads P(t) before the next product overwrites the buffer
+                    if (ok && t + 2 < n_half[g]) issue_qk(g, t + 2);
                 }
             }
             if (!ok) {
@@ -201,89 +204,54 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tS = tmem_base + lane_sel + g * 128;
         const uint32_t tO = tmem_base + lane_sel + 256 + g * 128;
-        uint8_t* sPg = sP + g * kExtTileBytes;
-        const int n_g = n_tiles[g];
+        const int n_g = n_half[g];
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
 
-        for (int j = 0; j < n_g; ++j) {
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_s[g], j & 1) && !ctl->abort);
+        for (int t = 0; t < n_g; ++t) {
+            const int bf = t & 1;
+            // S(t) complete; the product that wrote it was issued after P V(t - 2), so that one has read the buffer.
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_s[g][bf], (t >> 1) & 1) && !ctl->abort);
             if (!ok) break;
             tc_fence_after_sync();
-            const int col0 = j * kExtTile;
-            // Warp-uniform: only tiles on the diagonal (or holding the end of the request) need the comparison.
-            const bool masked = (col0 + kExtTile - 1 > first_limit) || !(p.scale_log2 > 0.f);
-            // The previous P V of this tile must be done before P is overwritten or O is touched.
-            if (j > 0) {
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_o[g], (j - 1) & 1) && !ctl->abort);
-                if (!ok) break;
-                tc_fence_after_sync();
-            }
-            // One pass over S in the common case: probabilities are formed against the maximum in use while
-            // the tile's own maximum is tracked; only when that one is more than the step above (or on the
-            // first tile) is the maximum moved, O and l rescaled, and the pass repeated.
-            float psum = 0.f, m_tile = -INFINITY;
-            auto sweep = [&](const float neg_m, const bool track) {
-                psum = 0.f;
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tS + c * 32, r);
-                    tmem_ld_wait();
-                    float pv[32];
-                    if (masked) {
+            const int col0 = t * kPpHalf;
+            const uint32_t tSb = tS + bf * kPpHalf;
+            // Warp-uniform: only half-tiles on the diagonal (or holding the end of the request) need the comparison.
+            const bool masked = (col0 + kPpHalf - 1 > first_limit) || !(p.scale_log2 > 0.f);
+            uint32_t r0[32], r1[32];                          // the row's 64 scores stay in registers
+            tmem_ld_32x32(tSb, r0);
+            tmem_ld_32x32(tSb + 32, r1);
+            tmem_ld_wait();
+            float m_tile = -INFINITY;
+            if (masked) {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const bool vis = col0 + c * 32 + i <= my_limit;
-                            const float sc = __uint_as_float(r[i]) * p.scale_log2;
-                            if (track && vis) m_tile = fmaxf(m_tile, sc);
-                            pv[i] = vis ? ex2_approx(sc + neg_m) : 0.f;
-                            psum += pv[i];
-                        }
-                    } else {
-                        float raw = -INFINITY;
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            if (track) raw = fmaxf(raw, __uint_as_float(r[i]));
-                            pv[i] = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-                            psum += pv[i];
-                        }
-                        if (track) m_tile = fmaxf(m_tile, raw * p.scale_log2);   // scale_log2 > 0 on this path
-                    }
-#pragma unroll
-                    for (int q8 = 0; q8 < 4; ++q8) {
-                        uint4 w;
-                        w.x = pack_bf16x2(pv[q8 * 8 + 0], pv[q8 * 8 + 1]);
-                        w.y = pack_bf16x2(pv[q8 * 8 + 2], pv[q8 * 8 + 3]);
-                        w.z = pack_bf16x2(pv[q8 * 8 + 4], pv[q8 * 8 + 5]);
-                        w.w = pack_bf16x2(pv[q8 * 8 + 6], pv[q8 * 8 + 7]);
-                        const int c8 = c * 4 + q8;             // 16-byte chunk within the 128-key row
-                        *reinterpret_cast<uint4*>(sPg + (c8 >> 3) * kExtHalfBytes + row * 128 + (((c8 & 7) ^ (row & 7)) << 4)) = w;
-                    }
-                }
-            };
-            if (j == 0) {
-                // No maximum yet: a tracking-only sweep would waste the exponentials, so find the maximum first.
-#pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tS + c * 32, r);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i)
-                        if (!masked || col0 + c * 32 + i <= my_limit) m_tile = fmaxf(m_tile, __uint_as_float(r[i]) * p.scale_log2);
+                for (int i = 0; i < 32; ++i) {
+                    if (col0 + i <= my_limit) m_tile = fmaxf(m_tile, __uint_as_float(r0[i]) * p.scale_log2);
+                    if (col0 + 32 + i <= my_limit) m_tile = fmaxf(m_tile, __uint_as_float(r1[i]) * p.scale_log2);
                 }
             } else {
-                sweep(-m_used, true);
+                float a0 = -INFINITY, a1 = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    a0 = fmaxf(a0, __uint_as_float(r0[i]));
+                    a1 = fmaxf(a1, __uint_as_float(r1[i]));
+                }
+                m_tile = fmaxf(a0, a1) * p.scale_log2;            // scale_log2 > 0 on this path
             }
+            // Move the reference maximum only when the true one is more than the step above it (warp-uniform):
+            // then O and l are rescaled; otherwise probabilities are formed against the old reference (<= 2^8).
             const bool grow = (m_tile > m_used + kPpRescaleStep) || (m_used == -INFINITY);
-            if (__any_sync(0xffffffffu, grow)) {                      // warp-uniform
+            if (__any_sync(0xffffffffu, grow)) {
                 float m_to = fmaxf(m_used, m_tile);
                 if (m_to == -INFINITY) m_to = 0.f;
-                const float alpha = exp2f(m_used - m_to);             // 0 on the first tile
+                const float alpha = exp2f(m_used - m_to);             // 0 on the first half-tile
                 l *= alpha;
                 m_used = m_to;
-                if (j > 0) {
+                if (t > 0) {
+                    // O must be at rest: P V(t - 1) is the last product issued for this tile.
+                    ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_o[g][(t - 1) & 1], ((t - 1) >> 1) & 1) && !ctl->abort);
+                    if (!ok) break;
+                    tc_fence_after_sync();
 #pragma unroll 1
                     for (int c = 0; c < 4; ++c) {
                         uint32_t r[32];
@@ -295,28 +263,57 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     }
                     tmem_st_wait();
                 }
-                sweep(-m_used, false);
             }
+            // Probabilities, packed two bf16 per 32-bit column, go back into the first 32 columns of the S buffer.
+            const float neg_m = -m_used;
+            uint32_t pk[32];
+            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float e0 = ex2_approx(fmaf(__uint_as_float(r0[i]), p.scale_log2, neg_m));
+                float e1 = ex2_approx(fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, neg_m));
+                float e2 = ex2_approx(fmaf(__uint_as_float(r1[i]), p.scale_log2, neg_m));
+                float e3 = ex2_approx(fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, neg_m));
+                if (masked) {
+                    if (col0 + i > my_limit) e0 = 0.f;
+                    if (col0 + i + 1 > my_limit) e1 = 0.f;
+                    if (col0 + 32 + i > my_limit) e2 = 0.f;
+                    if (col0 + 32 + i + 1 > my_limit) e3 = 0.f;
+                }
+                s4[0] += e0;
+                s4[1] += e1;
+                s4[2] += e2;
+                s4[3] += e3;
+                pk[i >> 1] = pack_bf16x2(e0, e1);
+                pk[16 + (i >> 1)] = pack_bf16x2(e2, e3);
+            }
+            const float psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            tmem_st_32x32(tSb, pk);
+            tmem_st_wait();
             l += psum;
             // Rows of the last tile past the request's last token may hold anything: V must be finite there
-            // because P (zero) still multiplies it.  Both groups write the same zeros.
-            const int tile_valid = s_total - col0;
-            if (tile_valid < kExtTile) {
-                uint8_t* sV = sRing + ((2 * j + 1) % kPpSlots) * kExtTileBytes;
-                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[(2 * j + 1) % kPpSlots], ((2 * j + 1) / kPpSlots) & 1));
+            // because P (zero) still multiplies it.  Done with the tile's first half; both groups write the same zeros.
+            const int tile_valid = s_total - (t >> 1) * kExtTile;
+            if (bf == 0 && tile_valid < kExtTile) {
+                const int q = 2 * (t >> 1) + 1;
+                uint8_t* sV = sRing + (q % kPpSlots) * kExtTileBytes;
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->full[q % kPpSlots], (q / kPpSlots) & 1) && !ctl->abort);
                 if (!ok) break;
                 for (int idx = row; idx < (kExtTile - tile_valid) * 16; idx += 128) {
                     const int r = tile_valid + idx / 16, c = idx % 16;
                     *reinterpret_cast<uint4*>(sV + (c >> 3) * kExtHalfBytes + r * 128 + ((c & 7) << 4)) = make_uint4(0, 0, 0, 0);
                 }
+                fence_proxy_async_smem();
             }
-            fence_proxy_async_smem();
             tc_fence_before_sync();
-            mbar_arrive(&ctl->bar_p[g]);
+            mbar_arrive(&ctl->bar_p[g][bf]);
         }
 
         if (ok) {
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_o[g], (n_g - 1) & 1) && !ctl->abort);
+            // The last two products (one per P buffer) end the accumulation.
+            if (n_g >= 2)
+                ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_o[g][(n_g - 2) & 1], ((n_g - 2) >> 1) & 1) && !ctl->abort);
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_o[g][(n_g - 1) & 1], ((n_g - 1) >> 1) & 1) && !ctl->abort);
             tc_fence_after_sync();
         }
         if (!ok) {
