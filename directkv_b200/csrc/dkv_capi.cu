@@ -512,6 +512,14 @@ int build_layer(LayerState* L, const dkv_layer_desc* d) {
     return DKV_OK;
 }
 
+#ifdef DKV_PP_TIMING
+unsigned long long* pp_timing_buffer() {
+    static unsigned long long* buf = nullptr;
+    if (!buf && (cudaMalloc(&buf, 64) != cudaSuccess || cudaMemset(buf, 0, 64) != cudaSuccess)) buf = nullptr;
+    return buf;
+}
+#endif
+
 // Projection of T rows of X with RoPE and write-back (tcgen05 kernel).
 int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int T, const int* tok_pos,
                       const int* tok_slot, bool store_pool, __nv_bfloat16* kv_new, float* splitk, cudaStream_t st) {
@@ -875,6 +883,18 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
     return launch_attention(ctx, L, ap, paged, mp, st, a->new_mode == DKV_NEW_PROJECT ? ctx->ev_join : nullptr);
 }
 
+#ifdef DKV_PP_TIMING
+// Instrumented builds only: cycle counters of extend_attn_pp_kernel (see the PP_ACC indices in dkv_extend_pp.cuh).
+extern "C" int dkv_debug_pp_timing(unsigned long long* out8, int reset) {
+    unsigned long long* d = pp_timing_buffer();
+    if (!d) return DKV_ERR_CUDA;
+    if (cudaDeviceSynchronize() != cudaSuccess) return DKV_ERR_CUDA;
+    if (out8 && cudaMemcpy(out8, d, 64, cudaMemcpyDeviceToHost) != cudaSuccess) return DKV_ERR_CUDA;
+    if (reset && cudaMemset(d, 0, 64) != cudaSuccess) return DKV_ERR_CUDA;
+    return DKV_OK;
+}
+#endif
+
 int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) { return decode_impl(ctx, a, stream, nullptr); }
 
 int dkv_exchange_create(dkv_context* ctx, int rank, int world, int64_t max_rows, dkv_exchange** out) {
@@ -1021,14 +1041,18 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
     extend_prep_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, st>>>(
         B, S_new, seqlen_past, n_past_blocks_dev, is_causal, row_map, L.d.row_stride, vseq, vrow, tok_pos, tok_slot);
     DKV_CUDA(cudaGetLastError());
-    PrepParams prep{};
-    prep.seq_lens = vseq;
-    prep.batch = static_cast<int>(rows);
-    prep.n_new = 0;
-    prep.cum_tiles = cum;
-    attn_prep_kernel<<<1, 256, 0, st>>>(prep);
-    DKV_CUDA(cudaGetLastError());
-    ctx->launches += 2;
+    ctx->launches += 1;
+    if (ctx->extend_rowwise) {
+        // Only the row-streamed path walks tile cursors: prefix sum of the virtual requests' tile counts.
+        PrepParams prep{};
+        prep.seq_lens = vseq;
+        prep.batch = static_cast<int>(rows);
+        prep.n_new = 0;
+        prep.cum_tiles = cum;
+        attn_prep_kernel<<<1, 256, 0, st>>>(prep);
+        DKV_CUDA(cudaGetLastError());
+        ctx->launches += 1;
+    }
     rc = launch_projection(ctx, L, X, static_cast<int>(rows), tok_pos, tok_slot, true, nullptr,
                            reinterpret_cast<float*>(base + sp.splitk), st);
     if (rc != DKV_OK) return rc;
@@ -1087,8 +1111,13 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         ep.scale_log2 = scale * 1.4426950408889634f;
         ep.out = static_cast<__nv_bfloat16*>(O);
         ep.status = ctx->status;
+#ifdef DKV_PP_TIMING
+        ep.timing = pp_timing_buffer();
+        ep.dbg_mode = getenv("DKV_PP_MODE") ? atoi(getenv("DKV_PP_MODE")) : 0;
+#endif
         if (ctx->extend_pingpong != 0) {
-            dim3 grid((S_new + 2 * TQ - 1) / (2 * TQ), nh_kv * nsub, B);
+            // Head slots vary fastest so that the longest (latest) query tiles of ALL heads are dispatched first.
+            dim3 grid(nh_kv * nsub, (S_new + 2 * TQ - 1) / (2 * TQ), B);
             extend_attn_pp_kernel<<<grid, kPpThreads, kPpSmem, st>>>(tmQ, *tmK, *tmV, ep);
         } else {
             dim3 grid((S_new + TQ - 1) / TQ, nh_kv * nsub, B);

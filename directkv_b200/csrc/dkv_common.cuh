@@ -23,6 +23,7 @@ enum StatusBits : unsigned int {
 
 // Upper bound for any device-side wait, in nanoseconds of %globaltimer.
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr long long kWaitLimitCycles = 4000000000ll;   // about 2 s at the B200's 1.9-2.0 GHz SM clock
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -67,7 +68,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
+#ifdef DKV_TEST_WAIT
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(ok)
@@ -78,14 +83,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Waits for the phase with the given parity.  Returns false when the time limit
 // ran out (the caller records the failure and stops issuing work).
+// The limit is counted on the SM's own cycle counter: reading it costs a few cycles, while a read of
+// %globaltimer on the path of every wait that is not satisfied at once costs about as much as the wait itself.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 256; ++i)
+        for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+        if (clock64() - t0 > kWaitLimitCycles) return false;
     }
 }
 
@@ -129,6 +136,14 @@ __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// Two non-negative finite floats to packed bf16 with integer instructions (round half up: add half an ulp of
+// bf16, keep the upper 16 bits).  The conversion instruction shares the special-function unit with ex2, which
+// is the busiest pipe of the softmax; these three run on the integer pipe.
+__device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
+    const uint32_t a = __float_as_uint(lo) + 0x8000u, b = __float_as_uint(hi) + 0x8000u;
+    return __byte_perm(a, b, 0x7632);
 }
 
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }

@@ -7,7 +7,7 @@
 // tiles and specialises its warps:
 //
 //   warp 0      TMA producer: both Q tiles once, then K(0), V(0), K(1), V(1), ... through a ring of 32 KB slots
-//   warp 1      MMA issuer (one thread): S_g = Q_g K^T and O_g += P_g V for g = 0, 1
+//   warps 1, 2  MMA issuers (one thread each): S_g = Q_g K^T and O_g += P_g V for tile g = 0 / 1
 //   warps 4-7   softmax of tile 0 (thread = query row = TMEM lane)
 //   warps 8-11  softmax of tile 1
 //
@@ -26,6 +26,22 @@
 
 #include "dkv_extend.cuh"
 
+#ifdef DKV_PP_TIMING
+#define PP_T0(var) const long long var = clock64()
+#define PP_ACC(idx, var) do { pp_acc[idx] += static_cast<unsigned long long>(clock64() - (var)); } while (0)
+#define PP_CNT(idx) do { pp_acc[idx] += 1ull; } while (0)
+#define PP_DECL unsigned long long pp_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PP_FLUSH do { if (lane == 0 && p.timing) for (int i_ = 0; i_ < 8; ++i_) if (pp_acc[i_]) atomicAdd(p.timing + i_, pp_acc[i_]); } while (0)
+#define PP_MODE(m) ((p.dbg_mode & (m)) != 0)
+#else
+#define PP_MODE(m) false
+#define PP_DECL
+#define PP_FLUSH
+#define PP_T0(var)
+#define PP_ACC(idx, var)
+#define PP_CNT(idx)
+#endif
+
 namespace dkv {
 
 constexpr int kPpSlots = 5;                                   // ring of [128 x 128] bf16 tiles: K and V alternate
@@ -39,7 +55,7 @@ struct PpCtrl {
     uint64_t full[kPpSlots];
     uint64_t empty[kPpSlots];
     uint64_t bar_s[2][2];     // [g][buf] S_g(t) complete, buf = t & 1
-    uint64_t bar_p[2][2];     // [g][buf] P_g(t) stored, S buffer consumed, O_g rescaled: 128 arrivals
+    uint64_t bar_p[2][2];     // [g][buf] P_g(t) stored, S buffer consumed, O_g rescaled: one arrival per softmax warp
     uint64_t bar_o[2][2];     // [g][buf] O_g += P_g(t) V complete
     uint32_t tmem;
     volatile int abort;
@@ -55,10 +71,11 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     PpCtrl* ctl = reinterpret_cast<PpCtrl*>(sRing + kPpSlots * kExtTileBytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    PP_DECL;
     const int G = p.G, TQ = kExtTile / G;
-    const int qt = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // longest (latest) tiles first
+    const int qt = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);   // longest (latest) tiles first
     const int b = blockIdx.z;
-    const int h = blockIdx.y / p.nsub, sub = blockIdx.y % p.nsub;
+    const int h = blockIdx.x / p.nsub, sub = blockIdx.x % p.nsub;
     const int qhead0 = h * p.g_total + sub * G;
     const int past = p.n_past_blocks ? p.n_past_blocks[0] * 64 : p.seqlen_past;
     const int q0 = qt * 2 * TQ;                               // first new token of tile 0; tile 1 starts at q0 + TQ
@@ -77,12 +94,12 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         mbar_init(&ctl->bar_q, 1);
         for (int s = 0; s < kPpSlots; ++s) {
             mbar_init(&ctl->full[s], 1);
-            mbar_init(&ctl->empty[s], 1);
+            mbar_init(&ctl->empty[s], 2);                     // one arrival per MMA issuer
         }
         for (int g = 0; g < 2; ++g)
             for (int bf = 0; bf < 2; ++bf) {
                 mbar_init(&ctl->bar_s[g][bf], 1);
-                mbar_init(&ctl->bar_p[g][bf], 128);
+                mbar_init(&ctl->bar_p[g][bf], 4);
                 mbar_init(&ctl->bar_o[g][bf], 1);
             }
         ctl->abort = 0;
@@ -112,12 +129,15 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tma_load_3d(sQ + g * kExtTileBytes + kExtHalfBytes, &tmQ, &ctl->bar_q, 64, qhead0, b * p.S_new + q0 + g * TQ);
             }
             for (int q = 0; q < 2 * n_max; ++q) {             // q even: K(q/2), odd: V(q/2)
+                if (PP_MODE(4)) break;
                 const int s = q % kPpSlots;
+                PP_T0(tp);
                 if (q >= kPpSlots && !mbar_wait_bounded(&ctl->empty[s], ((q / kPpSlots) - 1) & 1)) {
                     atomicOr(p.status, kStatusWaitTimeout);
                     ctl->abort = 1;
                     break;
                 }
+                PP_ACC(5, tp);
                 if (ctl->abort) break;
                 uint8_t* dst = sRing + s * kExtTileBytes;
                 const CUtensorMap* tm = (q & 1) ? &tmV : &tmK;
@@ -128,63 +148,75 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------ MMA issuer ------------------------------------------------
+    } else if (warp == 1 || warp == 2) {
+        // ------------------------------------------------ MMA issuers ------------------------------------------------
+        // One thread per query tile (warp 1: tile 0, warp 2: tile 1), so neither tile waits for the other's
+        // handshakes.  Descriptors are built once; inside the loops only constants are added to them.
         if (lane == 0) {
+            const int g = warp - 1;
+            const int n_g = n_half[g];
             constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(kExtTile, kPpHalf);
             constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(kExtTile, kExtTile) | (1u << 16);   // B (V) is MN-major
+            const uint64_t q_desc = umma_desc_k_sw128(smem_u32(sQ + g * kExtTileBytes));
+            const uint64_t k_desc0 = umma_desc_k_sw128(smem_u32(sRing));
+            const uint64_t v_desc0 = umma_desc_mn_sw128(smem_u32(sRing), kExtHalfBytes);
+            const uint32_t tS = tmem_base + g * 128, tO = tmem_base + 256 + g * 128;
             bool ok = mbar_wait_bounded(&ctl->bar_q, 0);
             int ring_ready = -1;                              // highest ring sequence number known to have landed
             auto wait_ring = [&](int q) {
+                if (PP_MODE(4)) return;
                 while (ok && ring_ready < q) {
                     const int nq = ring_ready + 1;
                     ok = mbar_wait_bounded(&ctl->full[nq % kPpSlots], (nq / kPpSlots) & 1);
                     ring_ready = nq;
                 }
-                tc_fence_after_sync();
             };
-            const int last1 = n_half[1] - 1;
-            auto issue_qk = [&](int g, int t) {               // S_g[t & 1] = Q_g K(rows 64 (t & 1) ... of tile t >> 1)^T
-                const int q = 2 * (t >> 1);
+            auto issue_qk = [&](int t) {                      // S[t & 1] = Q K(rows 64 (t & 1) ... of tile t >> 1)^T
+                const int q = 2 * (t >> 1), slot = q % kPpSlots;
                 wait_ring(q);
                 if (!ok) return;
-                const uint32_t qa = smem_u32(sQ + g * kExtTileBytes);
-                const uint32_t ka = smem_u32(sRing + (q % kPpSlots) * kExtTileBytes) + (t & 1) * kPpHalf * 128;
+                tc_fence_after_sync();
+                const uint64_t kd = k_desc0 + static_cast<uint64_t>((slot * kExtTileBytes + (t & 1) * kPpHalf * 128) >> 4);
+                const uint32_t d = tS + (t & 1) * kPpHalf;
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    const uint32_t off = (k >> 2) * kExtHalfBytes + (k & 3) * 32;
-                    umma_bf16_ss(tmem_base + g * 128 + (t & 1) * kPpHalf, umma_desc_k_sw128(qa + off),
-                                 umma_desc_k_sw128(ka + off), idesc_qk, k > 0 ? 1u : 0u);
+                    if (PP_MODE(2)) break;
+                    constexpr int unit = 16;                  // descriptor addresses count 16-byte units
+                    const uint64_t off = static_cast<uint64_t>(((k >> 2) * kExtHalfBytes + (k & 3) * 32) / unit);
+                    umma_bf16_ss(d, q_desc + off, kd + off, idesc_qk, k > 0 ? 1u : 0u);
                 }
                 umma_commit(&ctl->bar_s[g][t & 1]);
-                // Tile 1 issues last: its second half (or its very last half-tile) is the last reader of K(t >> 1).
-                if (g == 1 && ((t & 1) || t == last1)) umma_commit(&ctl->empty[q % kPpSlots]);
+                if (((t & 1) || t == n_g - 1) && !PP_MODE(4)) umma_commit(&ctl->empty[slot]);   // this tile's last read of K(t >> 1)
             };
-            auto issue_pv = [&](int g, int t) {               // O_g (+)= P_g[t & 1] V(rows 64 (t & 1) ... of tile t >> 1)
-                const int q = 2 * (t >> 1) + 1;
+            auto issue_pv = [&](int t) {                      // O (+)= P[t & 1] V(rows 64 (t & 1) ... of tile t >> 1)
+                const int q = 2 * (t >> 1) + 1, slot = q % kPpSlots;
                 wait_ring(q);
                 if (!ok) return;
-                const uint32_t pa = tmem_base + g * 128 + (t & 1) * kPpHalf;      // P lies over the S buffer it came from
-                const uint32_t va = smem_u32(sRing + (q % kPpSlots) * kExtTileBytes) + (t & 1) * kPpHalf * 128;
+                tc_fence_after_sync();
+                const uint64_t vd = v_desc0 + static_cast<uint64_t>((slot * kExtTileBytes + (t & 1) * kPpHalf * 128) >> 4);
+                const uint32_t pa = tS + (t & 1) * kPpHalf;   // P lies over the S buffer it came from
 #pragma unroll
-                for (int k = 0; k < 4; ++k)                   // 16 keys per step = 8 packed columns of P
-                    umma_bf16_ts(tmem_base + 256 + g * 128, pa + k * 8, umma_desc_mn_sw128(va + k * 16 * 128, kExtHalfBytes),
-                                 idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < 4; ++k)                   // 16 keys per step = 8 packed columns of P, 16 rows of V
+                    if (!PP_MODE(2)) umma_bf16_ts(tO, pa + k * 8, vd + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&ctl->bar_o[g][t & 1]);
-                if (g == 1 && ((t & 1) || t == last1)) umma_commit(&ctl->empty[q % kPpSlots]);
+                if (((t & 1) || t == n_g - 1) && !PP_MODE(4)) umma_commit(&ctl->empty[slot]);
             };
-            for (int t = 0; ok && t < 2; ++t)
-                for (int g = 0; ok && g < 2; ++g)
-                    if (t < n_half[g]) issue_qk(g, t);
-            for (int t = 0; ok && t < n_half[1]; ++t) {
-                for (int g = 0; ok && g < 2; ++g) {
-                    if (t >= n_half[g]) continue;
-                    ok = mbar_wait_bounded(&ctl->bar_p[g][t & 1], (t >> 1) & 1) && !ctl->abort;
-                    if (!ok) break;
-                    tc_fence_after_sync();
-                    issue_pv(g, t);                             // reads P(t) before the next product overwrites the buffer
-                    if (ok && t + 2 < n_half[g]) issue_qk(g, t + 2);
-                }
+            if (ok) issue_qk(0);
+            if (ok && n_g > 1) issue_qk(1);
+            for (int t = 0; ok && t < n_g; ++t) {
+                PP_T0(tw);
+                ok = mbar_wait_bounded(&ctl->bar_p[g][t & 1], (t >> 1) & 1) && !ctl->abort;
+                PP_ACC(3, tw);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_pv(t);                                  // reads P(t) before the next product overwrites the buffer
+                if (ok && t + 2 < n_g) issue_qk(t + 2);
+            }
+            // Tiles the other query tile still reads: every ring slot expects one arrival from each issuer.
+            for (int q = 2 * ((n_g + 1) >> 1); ok && q < 2 * n_max; ++q) {
+                if (PP_MODE(4)) break;
+                wait_ring(q);
+                if (ok) mbar_arrive(&ctl->empty[q % kPpSlots]);
             }
             if (!ok) {
                 atomicOr(p.status, kStatusWaitTimeout);
@@ -211,17 +243,30 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int t = 0; t < n_g; ++t) {
             const int bf = t & 1;
             // S(t) complete; the product that wrote it was issued after P V(t - 2), so that one has read the buffer.
+            PP_T0(ts);
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_s[g][bf], (t >> 1) & 1) && !ctl->abort);
+            PP_ACC(0, ts);
+            PP_CNT(7);
+            PP_T0(tc);
             if (!ok) break;
             tc_fence_after_sync();
             const int col0 = t * kPpHalf;
             const uint32_t tSb = tS + bf * kPpHalf;
             // Warp-uniform: only half-tiles on the diagonal (or holding the end of the request) need the comparison.
             const bool masked = (col0 + kPpHalf - 1 > first_limit) || !(p.scale_log2 > 0.f);
+            if (PP_MODE(1)) {
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl->bar_p[g][bf]);
+                continue;
+            }
             uint32_t r0[32], r1[32];                          // the row's 64 scores stay in registers
+            PP_T0(t_ld);
             tmem_ld_32x32(tSb, r0);
             tmem_ld_32x32(tSb + 32, r1);
             tmem_ld_wait();
+            PP_ACC(4, t_ld);
+            PP_T0(t_mx);
             float m_tile = -INFINITY;
             if (masked) {
 #pragma unroll
@@ -241,7 +286,9 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             // Move the reference maximum only when the true one is more than the step above it (warp-uniform):
             // then O and l are rescaled; otherwise probabilities are formed against the old reference (<= 2^8).
             const bool grow = (m_tile > m_used + kPpRescaleStep) || (m_used == -INFINITY);
-            if (__any_sync(0xffffffffu, grow)) {
+            const bool any_grow = __any_sync(0xffffffffu, grow);
+            PP_ACC(6, t_mx);
+            if (any_grow) {
                 float m_to = fmaxf(m_used, m_tile);
                 if (m_to == -INFINITY) m_to = 0.f;
                 const float alpha = exp2f(m_used - m_to);             // 0 on the first half-tile
@@ -265,6 +312,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
             }
             // Probabilities, packed two bf16 per 32-bit column, go back into the first 32 columns of the S buffer.
+            PP_T0(t_ex);
             const float neg_m = -m_used;
             uint32_t pk[32];
             float s4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -284,10 +332,11 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 s4[1] += e1;
                 s4[2] += e2;
                 s4[3] += e3;
-                pk[i >> 1] = pack_bf16x2(e0, e1);
-                pk[16 + (i >> 1)] = pack_bf16x2(e2, e3);
+                pk[i >> 1] = pack_bf16x2_alu(e0, e1);
+                pk[16 + (i >> 1)] = pack_bf16x2_alu(e2, e3);
             }
             const float psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            PP_ACC(2, t_ex);
             tmem_st_32x32(tSb, pk);
             tmem_st_wait();
             l += psum;
@@ -305,8 +354,11 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
                 fence_proxy_async_smem();
             }
+            // One arrival per warp: 32 lanes arriving on the same mbarrier would serialise.
             tc_fence_before_sync();
-            mbar_arrive(&ctl->bar_p[g][bf]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->bar_p[g][bf]);
+            PP_ACC(1, tc);
         }
 
         if (ok) {
@@ -343,6 +395,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
     }
 
+    PP_FLUSH;
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 512);
