@@ -143,6 +143,7 @@ struct dkv_context {
     int attn_ctas = 0;
     int proj_split_k = 0;
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
+    int proj_wide = 1;                  // 256-token projection tiles when there are more 128-token tiles than SMs
     int proj_decode = -1;               // -1: swapped-operand projection kernel when T <= 128; 0 never; 1 same as -1
     int attn_mma = -1;                  // -1: tensor-core inner product when 3..16 query heads share a KV head; 0 never; 1 always
     int extend_pingpong = 1;            // two query tiles per CTA with specialised warps (0: one tile, four warps)
@@ -334,7 +335,9 @@ cudaError_t attn_mma_set_attr() {
                                 static_cast<int>(attn_smem_bytes<1, NW, NST>()));
 }
 
-constexpr int kProjStages = 4;
+constexpr int kProjStages = 4;       // 48 KB stages (128 tokens per CTA)
+constexpr int kProjStagesWide = 3;   // 64 KB stages (256 tokens per CTA)
+static_assert(kProjStagesWide * (2 * kProjABytes + kProjBBytes) == kProjStages * kProjStage, "both forms use the same ring size");
 // stages | control (barriers, TMEM holder) | alignment slack; the epilogue re-uses the stage area for
 // the split-K sum tile (128 x 260 floats) followed by the 64 KB bf16 output staging tile.
 constexpr size_t kProjSmem = static_cast<size_t>(kProjStages) * kProjStage + 4096 + 1024 + 1024;
@@ -524,15 +527,19 @@ unsigned long long* pp_timing_buffer() {
 int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int T, const int* tok_pos,
                       const int* tok_slot, bool store_pool, __nv_bfloat16* kv_new, float* splitk, cudaStream_t st) {
     const bool small = T <= kPdMaxTokens && ctx->proj_decode != 0;
-    CUtensorMap tmX;
-    int rc = encode_operand_map(&tmX, x, T, L.d.hidden, small ? pd_padded_tokens(T) : 128);
-    if (rc != DKV_OK) return rc;
     ProjParams pp{};
     pp.T = T;
     pp.H = L.d.hidden;
     pp.nh_kv = L.d.nh_kv;
     if (small) proj_decode_split(ctx, L.d.nh_kv, L.d.hidden, &pp.split_k, &pp.chunks_per_split);
     else proj_split(ctx, T, L.d.nh_kv, L.d.hidden, &pp.split_k, &pp.chunks_per_split);
+    // More 128-token tiles than SMs (prefill sizes): 256 tokens per CTA, so the weights cross L2 once per 256.
+    const int tiles128 = (T + kProjBM - 1) / kProjBM;
+    const bool wide = !small && pp.split_k == 1 && ctx->proj_wide != 0 &&
+                      static_cast<long long>(tiles128) * L.d.nh_kv > ctx->sm_count;
+    CUtensorMap tmX;
+    int rc = encode_operand_map(&tmX, x, T, L.d.hidden, small ? pd_padded_tokens(T) : wide ? 256 : 128);
+    if (rc != DKV_OK) return rc;
     pp.tok_pos = tok_pos;
     pp.tok_slot = tok_slot;
     pp.cos_sin = L.d.cos_sin;
@@ -547,9 +554,12 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
     if (small) {
         dim3 grid(L.d.nh_kv, pp.split_k);
         proj_rope_decode_kernel<<<grid, 128, pd_smem_bytes(pd_padded_tokens(T)), st>>>(tmX, L.tmWk, L.tmWv, pp);
+    } else if (wide) {
+        dim3 grid(L.d.nh_kv, (tiles128 + 1) / 2, 1);
+        proj_rope_kernel<kProjStagesWide, 2><<<grid, 128, kProjSmem, st>>>(tmX, L.tmWk, L.tmWv, pp);
     } else {
-        dim3 grid(L.d.nh_kv, (T + kProjBM - 1) / kProjBM, pp.split_k);
-        proj_rope_kernel<kProjStages><<<grid, 128, kProjSmem, st>>>(tmX, L.tmWk, L.tmWv, pp);
+        dim3 grid(L.d.nh_kv, tiles128, pp.split_k);
+        proj_rope_kernel<kProjStages, 1><<<grid, 128, kProjSmem, st>>>(tmX, L.tmWk, L.tmWv, pp);
     }
     DKV_CUDA(cudaGetLastError());
     ctx->launches += 1;
@@ -647,7 +657,10 @@ int dkv_context_create(int device, dkv_context** out) {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(extend_attn_pp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPpSmem);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(proj_rope_kernel<kProjStages>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(proj_rope_kernel<kProjStages, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kProjSmem));
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(proj_rope_kernel<kProjStagesWide, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kProjSmem));
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(proj_rope_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -694,6 +707,8 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "attn_ctas")) {
         DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
         ctx->attn_ctas = value;
+    } else if (!strcmp(key, "proj_wide")) {
+        ctx->proj_wide = value != 0;
     } else if (!strcmp(key, "proj_decode")) {
         DKV_REQUIRE(value >= -1 && value <= 1, "proj_decode must be -1, 0 or 1");
         ctx->proj_decode = value;

@@ -47,7 +47,10 @@ struct ProjParams {
     unsigned int* status;
 };
 
-template <int NST>
+// MT = 128-token sub-tiles per CTA (1 or 2).  With two, a stage holds 32 KB of X next to the same 32 KB of
+// weights and both halves of the 512 TMEM columns are used, so the weights cross L2 -> SM once per 256 tokens:
+// at prefill sizes the kernel is bound by that traffic, not by the tensor pipe.
+template <int NST, int MT>
 __global__ void __launch_bounds__(128, 1)
 proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmWk,
                  const __grid_constant__ CUtensorMap tmWv, const ProjParams p) {
@@ -55,8 +58,9 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     // The swizzled operand tiles need 1024-byte alignment.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     // Control words sit behind the area the epilogue re-uses (sum tile + output staging = 198,656 B).
-    uint8_t* ctrl = smem + NST * kProjStage + 4096;
-    static_assert(NST * kProjStage + 4096 >= kProjBM * kProjAccStride * 4 + kProjBM * 512, "epilogue tiles overlap the control words");
+    constexpr int kStage = MT * kProjABytes + kProjBBytes;
+    uint8_t* ctrl = smem + NST * kStage + 4096;
+    static_assert(NST * kStage + 4096 >= kProjBM * kProjAccStride * 4 + kProjBM * 512, "epilogue tiles overlap the control words");
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
     uint64_t* empty_bar = full_bar + NST;
     uint64_t* accum_bar = empty_bar + NST;
@@ -64,7 +68,8 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     volatile int* flags = reinterpret_cast<volatile int*>(tmem_holder + 1);  // [0] abort, [1] is_last
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int h = blockIdx.x, mt = blockIdx.y, sp = blockIdx.z;
+    const int h = blockIdx.x, sp = blockIdx.z;
+    const int n_mtiles = static_cast<int>(gridDim.y) * MT;            // 128-token tiles over all CTAs
     const int nchunks = p.H / kProjBK;
     const int c0 = sp * p.chunks_per_split;
     const int c1 = (c0 + p.chunks_per_split < nchunks) ? c0 + p.chunks_per_split : nchunks;
@@ -86,7 +91,7 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         tma_prefetch_desc(&tmWv);
     }
     if (warp == 1) {
-        tmem_alloc(tmem_holder, kProjTmemCols);
+        tmem_alloc(tmem_holder, MT * kProjTmemCols);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -104,12 +109,12 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     flags[0] = 1;
                     break;
                 }
-                uint8_t* st = smem + s * kProjStage;
-                mbar_arrive_expect_tx(&full_bar[s], kProjStage);
+                uint8_t* st = smem + s * kStage;
+                mbar_arrive_expect_tx(&full_bar[s], kStage);
                 const int kc = (c0 + i) * kProjBK;
-                tma_load_2d(st, &tmX, &full_bar[s], kc, mt * kProjBM);
-                tma_load_2d(st + kProjABytes, &tmWk, &full_bar[s], kc, h * kProjHead);
-                tma_load_2d(st + kProjABytes + kProjBBytes / 2, &tmWv, &full_bar[s], kc, h * kProjHead);
+                tma_load_2d(st, &tmX, &full_bar[s], kc, static_cast<int>(blockIdx.y) * MT * kProjBM);   // box of MT * 128 rows
+                tma_load_2d(st + MT * kProjABytes, &tmWk, &full_bar[s], kc, h * kProjHead);
+                tma_load_2d(st + MT * kProjABytes + kProjBBytes / 2, &tmWv, &full_bar[s], kc, h * kProjHead);
             }
         }
         __syncwarp();
@@ -127,12 +132,15 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
                     break;
                 }
                 tc_fence_after_sync();
-                const uint32_t a_addr = smem_u32(smem + s * kProjStage);
+                const uint32_t a_addr = smem_u32(smem + s * kStage);
                 const uint64_t a_desc = umma_desc_k_sw128(a_addr);
-                const uint64_t b_desc = umma_desc_k_sw128(a_addr + kProjABytes);
+                const uint64_t b_desc = umma_desc_k_sw128(a_addr + MT * kProjABytes);
 #pragma unroll
                 for (int k4 = 0; k4 < kProjBK / 16; ++k4)
-                    umma_bf16_ss(tmem_base, a_desc + 2 * k4, b_desc + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+#pragma unroll
+                    for (int m = 0; m < MT; ++m)
+                        umma_bf16_ss(tmem_base + m * kProjTmemCols, a_desc + (m * kProjABytes) / 16 + 2 * k4, b_desc + 2 * k4, idesc,
+                                     (i > 0 || k4 > 0) ? 1u : 0u);
                 umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
             }
             if (ok) umma_commit(accum_bar);
@@ -152,15 +160,19 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     const bool aborted = (flags[0] != 0);  // uniform across the CTA
 
     const int row = warp * 32 + lane;
+#pragma unroll 1
+    for (int msub = 0; msub < MT; ++msub) {
+    const int mt = static_cast<int>(blockIdx.y) * MT + msub;          // 128-token tile of this pass
+    if (mt * kProjBM >= p.T) break;                                   // CTA-uniform
     const int token = mt * kProjBM + row;
-    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + msub * kProjTmemCols;
     uint8_t* stage_out = smem;  // [128 rows][512 B], 16-byte chunks XOR-swizzled by row (after the sum tile with split-K)
     bool finalize = !aborted;
 
     if (!aborted && p.split_k > 1) {
         // Dump this CTA's fp32 tile, then let the CTA that arrives last combine all slices.
         float* mine = p.splitk_scratch +
-                      ((static_cast<size_t>(sp) * gridDim.y + mt) * p.nh_kv + h) * (kProjBM * kProjBN) +
+                      ((static_cast<size_t>(sp) * n_mtiles + mt) * p.nh_kv + h) * (kProjBM * kProjBN) +
                       static_cast<size_t>(row) * kProjBN;
 #pragma unroll 1
         for (int c = 0; c < kProjBN / 32; ++c) {
@@ -193,7 +205,7 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     if (finalize && p.split_k > 1) {
         const int rows_valid = (p.T - mt * kProjBM) < kProjBM ? (p.T - mt * kProjBM) : kProjBM;
         const float* tile0 = p.splitk_scratch + ((static_cast<size_t>(mt)) * p.nh_kv + h) * (kProjBM * kProjBN);
-        const size_t slice_stride = static_cast<size_t>(gridDim.y) * p.nh_kv * (kProjBM * kProjBN);
+        const size_t slice_stride = static_cast<size_t>(n_mtiles) * p.nh_kv * (kProjBM * kProjBN);
         for (int idx = tid; idx < rows_valid * (kProjBN / 4); idx += 128) {
             const int r = idx / (kProjBN / 4), c4 = idx % (kProjBN / 4);
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -311,8 +323,11 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             }
         }
     }
+    __syncthreads();     // the next pass re-uses the shared-memory tiles and the flags
+    if (tid == 0) flags[1] = 0;
+    }
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, kProjTmemCols);
+    if (warp == 1) tmem_dealloc(tmem_base, MT * kProjTmemCols);
 }
 
 }  // namespace dkv

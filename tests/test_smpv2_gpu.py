@@ -79,6 +79,25 @@ def test_many_token_tiles_no_split_k():
     _run_fwd(X, Wk, Wv, Q, K, V, cs, True, 0)
 
 
+@pytest.mark.parametrize("S_new", [600, 700])
+def test_projection_wide_tiles(S_new):
+    """More 128-token tiles than SMs: the projection takes 256 tokens per CTA (two accumulators in TMEM); the last
+    CTA of a head holds one partial sub-tile (600 = 4 x 128 + 88) or two (700 = 5 x 128 + 60).  Compared with the
+    128-token form as well."""
+    ctx = get_context(0)
+    X, Wk, Wv, Q, K, V, cs = _rand_case(1, 32, 32, S_new, 0, 256, seed=61 + S_new)
+    _run_fwd(X, Wk, Wv, Q, K, V, cs, True, 0, kv_on_host=False)
+    pools = []
+    for wide in (1, 0):
+        ctx.set("proj_wide", wide)
+        Kd, Vd = K.clone().to(DEV), V.clone().to(DEV)
+        kernel.smpv2_fwd(X.to(DEV), Wk.to(DEV), Wv.to(DEV), Q.to(DEV), Kd, Vd, cs.to(DEV), SCALE, True, 0, -1)
+        pools.append((Kd.cpu(), Vd.cpu()))
+    ctx.set("proj_wide", 1)
+    ctx.raise_on_status()
+    assert torch.equal(pools[0][0], pools[1][0]) and torch.equal(pools[0][1], pools[1][1])
+
+
 def test_q_rotation_and_hbm_pool():
     X, Wk, Wv, Q, K, V, cs = _rand_case(1, 4, 4, 48, 80, 128, seed=77)
     _run_fwd(X, Wk, Wv, Q, K, V, cs, True, 80, q_pos_start=80, kv_on_host=False)
