@@ -348,14 +348,17 @@ struct ScratchPlan {
     size_t cum, tok_pos, tok_slot, vseq, vrow, partials, kv_new, splitk, q_rot, stage_k, stage_v, total;
 };
 
-bool use_mma(const dkv_context* ctx, int g_total) {
-    return ctx->attn_mma == 1 || (ctx->attn_mma < 0 && g_total >= 3);
+// The tensor-core form reads 128-byte row segments (two 64-column swizzled boxes per row); over PCIe those make
+// half-size read requests and cost 20 % of the link (40 against 51 GB/s), and the link, not the instruction
+// issue rate, bounds a host-resident pool: automatic choice only for pools in HBM.
+bool use_mma(const dkv_context* ctx, int g_total, bool pool_on_host) {
+    return ctx->attn_mma == 1 || (ctx->attn_mma < 0 && g_total >= 3 && !pool_on_host);
 }
 
 // Query heads that share one pass over a KV head: the mma kernel takes up to 16 rows (the largest divisor of
 // g_total that fits), the CUDA-core kernel 4, 2 or 1.
-int choose_g(const dkv_context* ctx, int g_total) {
-    if (use_mma(ctx, g_total)) {
+int choose_g(const dkv_context* ctx, int g_total, bool pool_on_host) {
+    if (use_mma(ctx, g_total, pool_on_host)) {
         int g = g_total < 16 ? g_total : 16;
         while (g_total % g != 0) --g;
         return g;
@@ -407,16 +410,22 @@ ScratchPlan plan_scratch(const dkv_context* ctx, int64_t rows, int nh_q, int nh_
                          bool with_qrot, size_t stage_bytes = 0) {
     ScratchPlan s{};
     const int g_total = nh_q / nh_kv;
-    const int G = choose_g(ctx, g_total);
-    const int nsub = g_total / G;
     const size_t total_warps = static_cast<size_t>(attn_cta_count(ctx)) * 16;  // upper bound over variants
+    // Partial records of whichever form of the streaming kernel runs (the choice depends on where the pool lives).
+    size_t partial_floats = 0;
+    for (int on_host = 0; on_host < 2; ++on_host) {
+        const int G = choose_g(ctx, g_total, on_host != 0);
+        const int nsub = g_total / G;
+        const size_t f = (total_warps + static_cast<size_t>(rows) * nh_kv * nsub) * G * kPartialStride;
+        partial_floats = f > partial_floats ? f : partial_floats;
+    }
     size_t off = 0;
     s.cum = off;      off += align256((rows + 1) * 4);
     s.tok_pos = off;  off += align256(rows * 4);
     s.tok_slot = off; off += align256(rows * 4);
     s.vseq = off;     off += align256(rows * 4);
     s.vrow = off;     off += align256(rows * 4);
-    s.partials = off; off += align256((total_warps + static_cast<size_t>(rows) * nh_kv * nsub) * G * kPartialStride * 4);
+    s.partials = off; off += align256(partial_floats * 4);
     s.kv_new = off;   off += align256(static_cast<size_t>(rows) * nh_kv * 256 * 2);
     s.splitk = off;
     if (with_proj && hidden > 0) {
@@ -568,8 +577,8 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
 
 int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool paged, const MergeParams& mp_in,
                      cudaStream_t st, cudaEvent_t join_before_merge = nullptr) {
-    const int G = choose_g(ctx, ap.g_total);
-    const bool mma = use_mma(ctx, ap.g_total);
+    const int G = choose_g(ctx, ap.g_total, L.pool_on_host);
+    const bool mma = use_mma(ctx, ap.g_total, L.pool_on_host);
     ap.nsub = ap.g_total / G;
     const int ctas = attn_cta_count(ctx);
     const int mma_variant = ctx->attn_variant < 0 ? 2 : ctx->attn_variant;

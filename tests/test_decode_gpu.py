@@ -213,6 +213,49 @@ def test_larger_ragged_batch_balance():
     _run_decode(_shape(128, 8, 2), lens, 16, cfg_id=6)
 
 
+def test_config2_full_size_properties():
+    """BASELINE config 2 at its full size (16 requests, ctx U[512,8192], 32 MHA heads, 16-token pages, about 1 GB
+    of KV, pool in HBM), checked through properties that do not need the CPU oracle at that size:
+      * doubling V doubles O bit-exactly (powers of two are exact in bf16 and fp32);
+      * moving every page to another slot (a different permutation of the same logical contents) leaves O
+        bit-identical: tiles, their order and every rounding point are the same;
+      * the two shortest requests agree with the oracle."""
+    shape = workloads.OPT_6_7B
+    lens = [n + 1 for n in workloads.ragged_lengths_uniform(16, 512, 8192, seed=4235)]
+    page = 16
+    case = workloads.make_decode_case(shape, lens, page, 1, DEV, kv_on_host=False)
+    q, sl, table = case["q"], case["seq_lens"], case["page_table"]
+    kernel.register_layer(61, case["k_pool"], case["v_pool"], page_size=page)
+    out1 = kernel.decode(61, q, sl, shape.scale, page_table=table).clone()
+    get_context(0).raise_on_status()
+
+    short = sorted(range(len(lens)), key=lambda i: lens[i])[:2]
+    ref = orc.decode_layer(None, None, None, q[short].cpu(), case["k_pool"].cpu(), case["v_pool"].cpu(),
+                           table[short].cpu(), [lens[i] for i in short], page, None, shape.scale)
+    assert_close(out1[short], ref.view_as(out1[short]), "O of the two shortest requests")
+
+    case["v_pool"].mul_(2)
+    out2 = kernel.decode(61, q, sl, shape.scale, page_table=table).clone()
+    assert torch.equal(out2.float(), out1.float() * 2), "O must double bit-exactly with V"
+    case["v_pool"].mul_(0.5)
+    kernel.unregister_layer(61)
+
+    # Same logical cache under another page permutation.
+    n_pages = case["k_pool"].shape[0] // page
+    g = torch.Generator().manual_seed(99)
+    perm = torch.cat([torch.zeros(1, dtype=torch.long), torch.randperm(n_pages - 1, generator=g) + 1]).to(DEV)  # page 0 stays reserved
+    k2 = torch.empty_like(case["k_pool"]).view(n_pages, page, shape.nh_kv, 128)
+    v2 = torch.empty_like(case["v_pool"]).view(n_pages, page, shape.nh_kv, 128)
+    k2[perm] = case["k_pool"].view(n_pages, page, shape.nh_kv, 128)
+    v2[perm] = case["v_pool"].view(n_pages, page, shape.nh_kv, 128)
+    table2 = perm[table.long()].to(torch.int32)
+    kernel.register_layer(62, k2.view(-1, shape.nh_kv, 128), v2.view(-1, shape.nh_kv, 128), page_size=page)
+    out3 = kernel.decode(62, q, sl, shape.scale, page_table=table2)
+    get_context(0).raise_on_status()
+    assert torch.equal(out3, out1), "O must not depend on where the pages live"
+    kernel.unregister_layer(62)
+
+
 def test_errors():
     with pytest.raises(RuntimeError, match="not registered"):
         kernel.decode(999, torch.zeros(1, 128, dtype=torch.bfloat16, device=DEV),
