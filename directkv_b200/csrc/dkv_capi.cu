@@ -257,14 +257,26 @@ __global__ void __launch_bounds__(128) scatter_rows_kernel(uint4* __restrict__ d
 __global__ void __launch_bounds__(256) stage_rows_kernel(uint4* __restrict__ k_dst, uint4* __restrict__ v_dst,
                                                          const uint4* __restrict__ k_src, const uint4* __restrict__ v_src,
                                                          const int* __restrict__ row_map, long long row_stride, int B,
-                                                         int s_total, int row_vec /* nh * 16 */) {
+                                                         int s_total, int row_vec /* nh * 16 */,
+                                                         const int* __restrict__ page_table, long long pt_stride,
+                                                         int page_shift) {
     const long long per_req = static_cast<long long>(s_total) * row_vec;
     const long long total = per_req * B;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const int b = static_cast<int>(i / per_req);
         const long long r = i - b * per_req;
-        const long long src = static_cast<long long>(row_map ? row_map[b] : b) * row_stride * row_vec + r;
+        const long long row = row_map ? row_map[b] : b;
+        long long src;
+        if (page_table != nullptr) {
+            // Paged pool: position -> slot through the request's row of the page table; the staged copy is contiguous.
+            const long long pos = r / row_vec;
+            const long long slot = (static_cast<long long>(page_table[row * pt_stride + (pos >> page_shift)]) << page_shift) +
+                                   (pos & ((1ll << page_shift) - 1));
+            src = slot * row_vec + (r - pos * row_vec);
+        } else {
+            src = row * row_stride * row_vec + r;
+        }
         k_dst[i] = __ldg(k_src + src);
         v_dst[i] = __ldg(v_src + src);
     }
@@ -1043,16 +1055,21 @@ int dkv_merge_partials(dkv_context* ctx, const float* parts, int nranks, int64_t
 // Shared by the eager and the graph-safe extend entry points.
 static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, const void* Q, void* O, int B, int S_new,
                       int nh_q, float scale, int is_causal, int seqlen_past, const int32_t* n_past_blocks_dev,
-                      int q_pos_start, const int32_t* row_map, cudaStream_t st) {
+                      int q_pos_start, const int32_t* row_map, cudaStream_t st, const int32_t* page_table = nullptr,
+                      long long pt_stride = 0) {
     const int nh_kv = L.d.nh_kv;
     const int64_t rows = static_cast<int64_t>(B) * S_new;
     const bool qrot = (L.d.cos_sin != nullptr && q_pos_start >= 0);
-    // Host pool, length known on the host, more than one query tile: stage the rows in HBM once.
+    const bool project = (X != nullptr);              // nullptr: the new rows are in the pool already
+    const bool paged = (page_table != nullptr);
+    // Host pool, length known on the host, more than one query tile: stage the rows in HBM once.  A paged pool is
+    // always staged: the gather through the page table makes the rows contiguous for the tensor-core kernel.
     const int s_total_host = seqlen_past + S_new;
-    const bool stage = !ctx->extend_rowwise && L.pool_on_host && n_past_blocks_dev == nullptr &&
-                       static_cast<long long>(S_new) * (nh_q / nh_kv) > kExtTile;
+    const bool tensor_path = !ctx->extend_rowwise || paged;
+    const bool stage = paged || (!ctx->extend_rowwise && L.pool_on_host && n_past_blocks_dev == nullptr &&
+                                 static_cast<long long>(S_new) * (nh_q / nh_kv) > kExtTile);
     const size_t stage_bytes = stage ? static_cast<size_t>(B) * s_total_host * nh_kv * 256 : 0;
-    ScratchPlan sp = plan_scratch(ctx, rows, nh_q, nh_kv, L.d.hidden, true, qrot, stage_bytes);
+    ScratchPlan sp = plan_scratch(ctx, rows, nh_q, nh_kv, L.d.hidden, project, qrot, stage_bytes);
     int rc = ensure_scratch(ctx, sp.total);
     if (rc != DKV_OK) return rc;
     uint8_t* base = ctx->scratch;
@@ -1061,12 +1078,14 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
     int* tok_slot = reinterpret_cast<int*>(base + sp.tok_slot);
     int* vseq = reinterpret_cast<int*>(base + sp.vseq);
     int* vrow = reinterpret_cast<int*>(base + sp.vrow);
+    if (paged && (project || n_past_blocks_dev != nullptr))
+        return fail(DKV_ERR_INVALID, "a paged pool is supported for attention over stored rows with a host-side length only");
 
     extend_prep_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, st>>>(
         B, S_new, seqlen_past, n_past_blocks_dev, is_causal, row_map, L.d.row_stride, vseq, vrow, tok_pos, tok_slot);
     DKV_CUDA(cudaGetLastError());
     ctx->launches += 1;
-    if (ctx->extend_rowwise) {
+    if (!tensor_path) {
         // Only the row-streamed path walks tile cursors: prefix sum of the virtual requests' tile counts.
         PrepParams prep{};
         prep.seq_lens = vseq;
@@ -1077,9 +1096,11 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         DKV_CUDA(cudaGetLastError());
         ctx->launches += 1;
     }
-    rc = launch_projection(ctx, L, X, static_cast<int>(rows), tok_pos, tok_slot, true, nullptr,
-                           reinterpret_cast<float*>(base + sp.splitk), st);
-    if (rc != DKV_OK) return rc;
+    if (project) {
+        rc = launch_projection(ctx, L, X, static_cast<int>(rows), tok_pos, tok_slot, true, nullptr,
+                               reinterpret_cast<float*>(base + sp.splitk), st);
+        if (rc != DKV_OK) return rc;
+    }
     const __nv_bfloat16* q_use = static_cast<const __nv_bfloat16*>(Q);
     if (qrot) {
         __nv_bfloat16* q_rot = reinterpret_cast<__nv_bfloat16*>(base + sp.q_rot);
@@ -1089,7 +1110,7 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         DKV_CUDA(cudaGetLastError());
         q_use = q_rot;
     }
-    if (!ctx->extend_rowwise) {
+    if (tensor_path) {
         // Tensor-core path: 128 query rows per CTA = G query heads x 128/G tokens of one KV head.
         const int g_total = nh_q / nh_kv;
         int G = 1;
@@ -1109,7 +1130,8 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
             uint4* vs = reinterpret_cast<uint4*>(base + sp.stage_v);
             stage_rows_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(ks, vs, static_cast<const uint4*>(L.k_dev),
                                                                  static_cast<const uint4*>(L.v_dev), row_map,
-                                                                 L.d.row_stride, B, s_total_host, nh_kv * 16);
+                                                                 L.d.row_stride, B, s_total_host, nh_kv * 16, page_table,
+                                                                 pt_stride, L.page_shift);
             DKV_CUDA(cudaGetLastError());
             ctx->launches += 1;
             const int64_t srows = static_cast<int64_t>(B) * s_total_host;
@@ -1247,6 +1269,33 @@ int dkv_extend(dkv_context* ctx, int layer_id, const void* X, const void* Q, voi
     DKV_CUDA(cudaSetDevice(ctx->device));
     return run_extend(ctx, L, X, Q, O, B, S_new, nh_q, softmax_scale, is_causal, seqlen_past, nullptr, q_pos_start,
                       row_map, static_cast<cudaStream_t>(stream));
+}
+
+int dkv_extend_attend(dkv_context* ctx, int layer_id, const void* Q, void* O, int B, int S_new, int nh_q,
+                      float softmax_scale, int is_causal, int seqlen_past, const int32_t* row_map,
+                      const int32_t* page_table, int64_t pt_stride, void* stream) {
+    DKV_REQUIRE(ctx != nullptr, "ctx is NULL");
+    auto it = ctx->layers.find(layer_id);
+    if (it == ctx->layers.end())
+        return fail(DKV_ERR_NOT_REGISTERED, "dkv_extend_attend: layer %d not registered - call dkv_layer_register first",
+                    layer_id);
+    const LayerState& L = it->second;
+    DKV_REQUIRE(Q && O, "NULL tensor pointer");
+    DKV_REQUIRE(B > 0 && S_new > 0 && nh_q > 0 && nh_q % L.d.nh_kv == 0, "bad sizes");
+    DKV_REQUIRE(seqlen_past >= 0, "seqlen_past must be >= 0");
+    if (page_table != nullptr) {
+        DKV_REQUIRE(pt_stride > 0, "pt_stride must be positive with a page table");
+        DKV_REQUIRE(((static_cast<int64_t>(seqlen_past) + S_new - 1) >> L.page_shift) < pt_stride,
+                    "seqlen_past + S_new (%d) does not fit a page-table row of %lld pages", seqlen_past + S_new,
+                    (long long)pt_stride);
+    } else {
+        DKV_REQUIRE(L.d.row_stride > 0, "layer %d was registered without row_stride and no page table was given", layer_id);
+        DKV_REQUIRE(seqlen_past + S_new <= L.d.row_stride, "seqlen_past + S_new (%d) exceeds the pool row (%lld)",
+                    seqlen_past + S_new, (long long)L.d.row_stride);
+    }
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    return run_extend(ctx, L, nullptr, Q, O, B, S_new, nh_q, softmax_scale, is_causal, seqlen_past, nullptr, -1, row_map,
+                      static_cast<cudaStream_t>(stream), page_table, pt_stride);
 }
 
 int dkv_scatter_kv(dkv_context* ctx, void* k_pool, void* v_pool, int64_t n_slots, int64_t k_row_bytes,

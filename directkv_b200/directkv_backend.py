@@ -367,12 +367,34 @@ class DirectKVBackend(AttentionBackend):
         eng = self._token_layer(layer, forward_batch)
         ext = meta.extend_seq_lens_cpu or [meta.seq_lens_cpu[i] for i in range(bs)]
         pre = meta.extend_prefix_lens_cpu or [0] * bs
-        vlen, vrow = [], []
+        table = forward_batch.req_to_token_pool.req_to_token
+        g_total = nh_q // self.num_kv_heads
+        out = torch.empty(q.shape[0], nh_q * d, dtype=q.dtype, device=q.device)
+        # A request whose new rows fill at least one 128-row query tile goes to the tensor-core extend kernel
+        # (its rows are gathered through req_to_token once); shorter ones are batched as one virtual decode
+        # request per new row.
+        vlen, vrow, vidx = [], [], []
+        off = 0
         for i in range(bs):
-            vlen += [int(pre[i]) + j + 1 for j in range(int(ext[i]))]
-            vrow += [meta.req_pool_indices_cpu[i]] * int(ext[i])
-        vlen_t = torch.tensor(vlen, dtype=torch.int32).to(self.device, non_blocking=True)
-        vrow_t = torch.tensor(vrow, dtype=torch.int32).to(self.device, non_blocking=True)
-        q2 = q.reshape(-1, nh_q * d).contiguous()
-        return kernel.decode(eng, q2, vlen_t, float(layer.scaling),
-                             page_table=forward_batch.req_to_token_pool.req_to_token, row_map=vrow_t)
+            n_new, n_pre = int(ext[i]), int(pre[i])
+            if n_new * g_total >= 128:
+                q_i = q[off:off + n_new].reshape(1, n_new, nh_q, d).contiguous()
+                o_i = kernel.extend_attend(eng, q_i, float(layer.scaling), True, n_pre,
+                                           row_map=meta.req_idx_dev[i:i + 1], page_table=table)
+                out[off:off + n_new] = o_i.view(n_new, nh_q * d)
+            else:
+                vlen += [n_pre + j + 1 for j in range(n_new)]
+                vrow += [meta.req_pool_indices_cpu[i]] * n_new
+                vidx += list(range(off, off + n_new))
+            off += n_new
+        if vlen:
+            vlen_t = torch.tensor(vlen, dtype=torch.int32).to(self.device, non_blocking=True)
+            vrow_t = torch.tensor(vrow, dtype=torch.int32).to(self.device, non_blocking=True)
+            q2 = q.reshape(-1, nh_q * d)
+            if len(vidx) != q2.shape[0]:
+                idx = torch.tensor(vidx, dtype=torch.long, device=q.device)
+                o_small = kernel.decode(eng, q2[idx].contiguous(), vlen_t, float(layer.scaling), page_table=table, row_map=vrow_t)
+                out[idx] = o_small
+            else:
+                out = kernel.decode(eng, q2.contiguous(), vlen_t, float(layer.scaling), page_table=table, row_map=vrow_t)
+        return out

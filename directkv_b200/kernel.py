@@ -211,6 +211,38 @@ def extend(
     return out
 
 
+def extend_attend(
+    layer_id: int,
+    Q: torch.Tensor,                  # [B, S_new, NH_q, 128] bf16 CUDA
+    softmax_scale: float,
+    is_causal: bool,
+    seqlen_past: int,
+    row_map: Optional[torch.Tensor] = None,      # [B] int32 CUDA: pool row / page-table row of each request
+    page_table: Optional[torch.Tensor] = None,   # [rows, max_pages] int32 CUDA (page size of the registered layer)
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Attention of new rows that are already stored in the pool (``dkv_extend_attend``): the engine's form of
+    ``_sdpa_extend_manual`` (directkv/directkv_backend.py:861-891) on the tensor-core extend kernel."""
+    _check_cuda_bf16(Q, "Q")
+    _chk(Q.dim() == 4 and Q.size(3) == HEAD_DIM, "Q must be [B,S_new,NH_q,128]")
+    B, S_new = Q.size(0), Q.size(1)
+    if row_map is not None:
+        _chk(row_map.is_cuda and row_map.dtype == torch.int32 and row_map.numel() == B, "row_map must be [B] int32 CUDA")
+    pt_stride = 0
+    if page_table is not None:
+        _chk(page_table.is_cuda and page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1,
+             "page_table must be a 2-D int32 CUDA tensor with unit inner stride")
+        pt_stride = page_table.stride(0)
+    if out is None:
+        out = torch.empty_like(Q)
+    _check_cuda_bf16(out, "out")
+    ctx = get_context(Q.device.index)
+    _lib.check(_lib.load().dkv_extend_attend(
+        ctx.handle, int(layer_id), _ptr(Q), _ptr(out), B, S_new, Q.size(2), float(softmax_scale),
+        1 if is_causal else 0, int(seqlen_past), _ptr(row_map), _ptr(page_table), int(pt_stride), _stream()))
+    return out
+
+
 def decode_noalloc(
     k_pool: torch.Tensor,        # [n_slots, NH_kv, 128] bf16, pinned CPU or CUDA
     v_pool: torch.Tensor,

@@ -213,6 +213,20 @@ int dkv_extend(dkv_context* ctx, int layer_id, const void* X, const void* Q, voi
                void* stream);
 
 /*
+ * Attention of S_new rows that are ALREADY in the pool (stored by dkv_scatter_kv / set_kv_buffer) over
+ * positions [0, seqlen_past + i] of their request, on the tensor-core extend kernel: the engine's form of
+ * _sdpa_extend_manual (directkv/directkv_backend.py:861-891: gather req_to_token[req, :prefix + i + 1], triu mask
+ * with diagonal prefix + 1).  page_table == NULL: contiguous rows (slot = row_map[b] * row_stride + position).
+ * page_table [rows, pt_stride] int32 device: slot = page_table[row_map[b], position / page] * page + position % page
+ * with the layer's page size (1 for SGLang's req_to_token); the request's rows are gathered once into a
+ * contiguous staging tensor in HBM, which the kernel then reads once per 256 query rows.
+ * Q/O [B, S_new, nh_q, 128] bf16 device.
+ */
+int dkv_extend_attend(dkv_context* ctx, int layer_id, const void* Q, void* O, int B, int S_new, int nh_q,
+                      float softmax_scale, int is_causal, int seqlen_past, const int32_t* row_map,
+                      const int32_t* page_table, int64_t pt_stride, void* stream);
+
+/*
  * Stream-ordered store of new tokens into a token-indexed pool: replaces the blocking
  * device-to-host copy plus CPU scatter of DirectKVTokenToKVPool.set_kv_buffer
  * (directkv/directkv_pool.py:174-209).  Row i of cache_k / cache_v ([n_tokens, row_bytes],

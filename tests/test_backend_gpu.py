@@ -213,6 +213,34 @@ def test_token_pool_path_when_no_hidden_states():
     assert torch.equal(pool.get_key_buffer(1)[loc.cpu()], k.view(-1, NH_KV, D))
 
 
+def test_token_pool_chunked_prefill():
+    """Token pool, one request prefilled in two chunks (200 rows, then 100 more on a prefix of 200): both chunks are
+    long enough for the tensor-core kernel, which reads the rows through req_to_token."""
+    from directkv_b200 import DirectKVTokenToKVPool
+
+    be, runner, model, _ = _setup(theta=None)
+    g = torch.Generator().manual_seed(19)
+    pool = DirectKVTokenToKVPool(size=700, page_size=1, dtype=torch.bfloat16, head_num=NH_KV, head_dim=D,
+                                 layer_num=LAYERS, start_layer=0, end_layer=LAYERS - 1)
+    r2t = runner.req_to_token_pool
+    perm = (torch.randperm(700, generator=g) + 1).int()
+    r2t.req_to_token[3, :300] = perm[:300].to(DEV)
+    layer = model.layers[0]
+    k_ref = torch.zeros(701, NH_KV, D, dtype=torch.bfloat16)
+    v_ref = torch.zeros(701, NH_KV, D, dtype=torch.bfloat16)
+    for pre, n in ((0, 200), (200, 100)):
+        loc = r2t.req_to_token[3, pre:pre + n].long()
+        fb = make_batch(EXTEND, [pre + n], [3], DEV, extend_lens=[n], prefix_lens=[pre], token_pool=pool,
+                        req_to_token_pool=r2t, out_cache_loc=loc)
+        be.init_forward_metadata(fb)
+        q, k, v = _rand((n, NH_Q * D), g), _rand((n, NH_KV * D), g, 0.5), _rand((n, NH_KV * D), g, 0.5)
+        out = be.forward_extend(q.to(DEV), k.to(DEV), v.to(DEV), layer.attn, fb)
+        k_ref[loc.cpu()], v_ref[loc.cpu()] = k.view(-1, NH_KV, D), v.view(-1, NH_KV, D)
+        slots = r2t.req_to_token[3, :pre + n].long().cpu()
+        exp = orc.sdpa_extend(q.view(n, NH_Q, D), k_ref[slots], v_ref[slots], pre, D ** -0.5)
+        assert_close(out, exp.reshape(n, -1), f"chunk at prefix {pre}")
+
+
 def test_set_kv_buffer_scatter_kernel_matches_host_path():
     from directkv_b200 import DirectKVTokenToKVPool
 

@@ -207,6 +207,55 @@ def test_extend_large_scores_rescale():
     _run_fwd(X, Wk, Wv, Q, K, V, cs, True, S_past, kv_on_host=False)
 
 
+@pytest.mark.parametrize("page_size,host", [(1, True), (1, False), (16, True), (64, False)])
+@pytest.mark.parametrize("S_new,S_past", [(200, 0), (130, 333)])
+def test_extend_attend_paged_pool(page_size, host, S_new, S_past):
+    """Attention of rows already stored in a paged pool (the token pool with page size 1 is SGLang's req_to_token):
+    the rows are gathered through the page table into a contiguous staging tensor, then the tensor-core kernel."""
+    nh_q, nh_kv, B = 8, 2, 2
+    total = S_past + S_new
+    pages_per_req = (total + page_size - 1) // page_size
+    n_pages = B * pages_per_req + 3
+    g = torch.Generator().manual_seed(500 + page_size + S_new)
+    perm = (torch.randperm(n_pages - 1, generator=g) + 1).int()                   # page 0 stays unused
+    table = torch.zeros(B + 1, pages_per_req + 2, dtype=torch.int32)
+    rows = [2, 0]                                                                 # page-table row of each request
+    for b, r in enumerate(rows):
+        table[r, :pages_per_req] = perm[b * pages_per_req:(b + 1) * pages_per_req]
+    k_pool = (torch.randn(n_pages * page_size, nh_kv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    v_pool = (torch.randn(n_pages * page_size, nh_kv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    Q = torch.randn(B, S_new, nh_q, 128, generator=g).to(torch.bfloat16)
+    kd, vd = (k_pool.pin_memory(), v_pool.pin_memory()) if host else (k_pool.to(DEV), v_pool.to(DEV))
+    kernel.register_layer(71, kd, vd, page_size=page_size)
+    out = kernel.extend_attend(71, Q.to(DEV), SCALE, True, S_past, row_map=torch.tensor(rows, dtype=torch.int32, device=DEV),
+                               page_table=table.to(DEV))
+    get_context(0).raise_on_status()
+    for b, r in enumerate(rows):
+        pos = torch.arange(total)
+        slots = table[r, pos // page_size].long() * page_size + pos % page_size
+        ref = orc.sdpa_extend(Q[b], k_pool[slots], v_pool[slots], S_past, SCALE)
+        assert_close(out[b], ref, f"request {b}")
+    kernel.unregister_layer(71)
+
+
+def test_extend_attend_contiguous_rows_and_errors():
+    nh_q, nh_kv, rows, s_pad, S_new, S_past = 4, 4, 3, 512, 140, 60
+    g = torch.Generator().manual_seed(77)
+    K = (torch.randn(rows, s_pad, nh_kv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    V = (torch.randn(rows, s_pad, nh_kv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    Q = torch.randn(1, S_new, nh_q, 128, generator=g).to(torch.bfloat16)
+    kernel.register_layer(72, K.to(DEV), V.to(DEV), row_stride=s_pad)
+    out = kernel.extend_attend(72, Q.to(DEV), SCALE, True, S_past, row_map=torch.tensor([1], dtype=torch.int32, device=DEV))
+    get_context(0).raise_on_status()
+    ref = orc.sdpa_extend(Q[0], K[1, :S_past + S_new], V[1, :S_past + S_new], S_past, SCALE)
+    assert_close(out[0], ref, "O")
+    with pytest.raises(RuntimeError, match="exceeds the pool row"):
+        kernel.extend_attend(72, Q.to(DEV), SCALE, True, s_pad, row_map=torch.tensor([1], dtype=torch.int32, device=DEV))
+    kernel.unregister_layer(72)
+    with pytest.raises(RuntimeError, match="not registered"):
+        kernel.extend_attend(72, Q.to(DEV), SCALE, True, 0)
+
+
 def test_extend_paths_agree():
     """The tensor-core extend kernel and the row-streamed path (decode kernels, one virtual request per new
     row) implement the same function: compare them directly, non-causal included."""
