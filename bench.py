@@ -399,7 +399,7 @@ def main():
                     help="hbm / host: time only that mode of the decode step; extend: time the chunked-prefill path "
                          "(Llama-3-8B layer, 4096 new tokens) - short runs for profiler captures")
     ap.add_argument("--sweep", default=None, help="comma list of C1,C2,C3,C4,C5: run those configurations instead")
-    ap.add_argument("--sweep-out", default="gpurun_out/sweep.jsonl")
+    ap.add_argument("--sweep-out", default="sweep.jsonl")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

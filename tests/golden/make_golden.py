@@ -289,7 +289,9 @@ def gen_torch_paths(ref_dir, out):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py <checkout of the reference project>")
+    ref = sys.argv[1]
     install_stubs()
     gen_token_pool(ref, HERE)
     gen_request_pool(ref, HERE)
