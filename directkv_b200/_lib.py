@@ -131,6 +131,8 @@ SIGNATURES = {
                              C.c_float, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "dkv_extend_attend": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float,
                                     C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "dkv_extend_ragged": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                    C.c_void_p, C.c_int, C.c_float, C.c_int, C.c_void_p, C.c_int64, C.c_void_p]),
     "dkv_scatter_kv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
                                  C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "dkv_decode_noalloc": (C.c_int, [C.POINTER(NoAllocArgs), C.c_void_p]),

@@ -8,6 +8,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <algorithm>
 #include <map>
 #include <string>
 #include <utility>
@@ -153,6 +154,12 @@ struct dkv_context {
     int profile_attn = 0;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> attn_events;
     size_t attn_events_used = 0;
+    // Per-request metadata of a ragged extend: pinned host mirror, device copy, and the event of the last upload.
+    int* ragged_host = nullptr;
+    int* ragged_dev = nullptr;
+    size_t ragged_ints = 0;
+    cudaEvent_t ev_ragged = nullptr;
+    bool ragged_pending = false;
 };
 
 // Peer-memory exchange of sequence-split partials (one per process group of <= 8 GPUs of a box).
@@ -188,6 +195,57 @@ __global__ void extend_prep_kernel(int B, int S_new, int seqlen_past_host, const
     vrow[v] = row;
     tok_pos[v] = past + i;
     tok_slot[v] = static_cast<int>(static_cast<long long>(row) * row_stride + past + i);
+}
+
+// Largest b with prefix[b] <= v (prefix ascending, prefix[0] == 0).
+__device__ __forceinline__ int find_request(const int* __restrict__ prefix, int n, long long v) {
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (prefix[mid] <= v) lo = mid;
+        else hi = mid - 1;
+    }
+    return lo;
+}
+
+// Ragged extend: position and pool slot of every new row of the packed batch.
+__global__ void extend_prep_ragged_kernel(int B, int T, const int* __restrict__ q_row0, const int* __restrict__ past,
+                                          const int* __restrict__ rows, long long row_stride, int* __restrict__ tok_pos,
+                                          int* __restrict__ tok_slot) {
+    const int v = blockIdx.x * blockDim.x + threadIdx.x;
+    if (v >= T) return;
+    const int b = find_request(q_row0, B, v);
+    const int i = v - q_row0[b];
+    tok_pos[v] = past[b] + i;
+    tok_slot[v] = static_cast<int>(static_cast<long long>(rows[b]) * row_stride + past[b] + i);
+}
+
+// Ragged extend over a host or paged pool: rows [0, past_b + s_new_b) of every request, one after the other, into
+// a contiguous device staging tensor (request b starts at row kv_off[b]).
+__global__ void __launch_bounds__(256) stage_rows_ragged_kernel(uint4* __restrict__ k_dst, uint4* __restrict__ v_dst,
+                                                                const uint4* __restrict__ k_src,
+                                                                const uint4* __restrict__ v_src, int B,
+                                                                const int* __restrict__ kv_off,
+                                                                const int* __restrict__ rows, long long row_stride,
+                                                                int row_vec, const int* __restrict__ page_table,
+                                                                long long pt_stride, int page_shift) {
+    const long long total = static_cast<long long>(kv_off[B]) * row_vec;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long srow = i / row_vec;
+        const int b = find_request(kv_off, B, srow);
+        const long long pos = srow - kv_off[b];
+        const long long row = rows[b];
+        long long slot;
+        if (page_table != nullptr)
+            slot = (static_cast<long long>(page_table[row * pt_stride + (pos >> page_shift)]) << page_shift) +
+                   (pos & ((1ll << page_shift) - 1));
+        else
+            slot = row * row_stride + pos;
+        const long long src = slot * row_vec + (i - srow * row_vec);
+        k_dst[i] = __ldg(k_src + src);
+        v_dst[i] = __ldg(v_src + src);
+    }
 }
 
 // DKV_NEW_GIVEN: pack the caller's K/V rows into kv_new [B, nh, 2, 128] and store them to the pool.
@@ -706,6 +764,9 @@ int dkv_context_destroy(dkv_context* ctx) {
     if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
     if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->ragged_host) cudaFreeHost(ctx->ragged_host);
+    if (ctx->ragged_dev) cudaFree(ctx->ragged_dev);
+    if (ctx->ev_ragged) cudaEventDestroy(ctx->ev_ragged);
     if (ctx->status) cudaFree(ctx->status);
     if (ctx->counters) cudaFree(ctx->counters);
     delete ctx;
@@ -1296,6 +1357,175 @@ int dkv_extend_attend(dkv_context* ctx, int layer_id, const void* Q, void* O, in
     DKV_CUDA(cudaSetDevice(ctx->device));
     return run_extend(ctx, L, nullptr, Q, O, B, S_new, nh_q, softmax_scale, is_causal, seqlen_past, nullptr, -1, row_map,
                       static_cast<cudaStream_t>(stream), page_table, pt_stride);
+}
+
+// Grows the pinned host mirror and the device copy of the ragged-extend metadata (outside graph capture).
+static int ensure_ragged(dkv_context* ctx, size_t ints) {
+    if (ctx->ev_ragged == nullptr) DKV_CUDA(cudaEventCreateWithFlags(&ctx->ev_ragged, cudaEventDisableTiming));
+    if (ints <= ctx->ragged_ints) return DKV_OK;
+    if (ctx->ragged_pending) {
+        DKV_CUDA(cudaEventSynchronize(ctx->ev_ragged));
+        ctx->ragged_pending = false;
+    }
+    DKV_CUDA(cudaDeviceSynchronize());   // earlier launches may still read the old device copy
+    if (ctx->ragged_host) cudaFreeHost(ctx->ragged_host);
+    if (ctx->ragged_dev) cudaFree(ctx->ragged_dev);
+    ctx->ragged_host = nullptr;
+    ctx->ragged_dev = nullptr;
+    ctx->ragged_ints = 0;
+    const size_t want = ints + ints / 2 + 1024;
+    DKV_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&ctx->ragged_host), want * sizeof(int), cudaHostAllocDefault));
+    DKV_CUDA(cudaMalloc(reinterpret_cast<void**>(&ctx->ragged_dev), want * sizeof(int)));
+    ctx->ragged_ints = want;
+    return DKV_OK;
+}
+
+int dkv_extend_ragged(dkv_context* ctx, int layer_id, const void* X, const void* Q, void* O, int B,
+                      const int32_t* s_new_host, const int32_t* past_host, const int32_t* rows_host, int nh_q,
+                      float softmax_scale, int is_causal, const int32_t* page_table, int64_t pt_stride, void* stream) {
+    DKV_REQUIRE(ctx != nullptr, "ctx is NULL");
+    auto it = ctx->layers.find(layer_id);
+    if (it == ctx->layers.end())
+        return fail(DKV_ERR_NOT_REGISTERED, "dkv_extend_ragged: layer %d not registered - call dkv_layer_register first",
+                    layer_id);
+    const LayerState& L = it->second;
+    DKV_REQUIRE(Q && O && s_new_host && past_host && rows_host, "NULL argument");
+    DKV_REQUIRE(B > 0 && nh_q > 0 && nh_q % L.d.nh_kv == 0, "bad sizes");
+    const bool project = (X != nullptr), paged = (page_table != nullptr);
+    if (project) DKV_REQUIRE(L.has_weights, "layer %d has no projection weights registered", layer_id);
+    DKV_REQUIRE(!(project && paged), "projection into a paged pool is not supported: store the rows, then pass X = NULL");
+    if (paged) DKV_REQUIRE(pt_stride > 0, "pt_stride must be positive with a page table");
+    else DKV_REQUIRE(L.d.row_stride > 0, "layer %d was registered without row_stride and no page table was given", layer_id);
+    const int nh_kv = L.d.nh_kv;
+    const int g_total = nh_q / nh_kv;
+    int G = 1;
+    while (G < 128 && g_total % (2 * G) == 0) G *= 2;
+    const int nsub = g_total / G, TQ = kExtTile / G;
+
+    long long T = 0, kv_total = 0, n_items = 0;
+    for (int b = 0; b < B; ++b) {
+        DKV_REQUIRE(s_new_host[b] > 0 && past_host[b] >= 0 && rows_host[b] >= 0, "request %d: bad lengths or row", b);
+        const long long tot = static_cast<long long>(past_host[b]) + s_new_host[b];
+        if (paged) DKV_REQUIRE(((tot - 1) >> L.page_shift) < pt_stride, "request %d does not fit a page-table row", b);
+        else DKV_REQUIRE(tot <= L.d.row_stride, "request %d: seqlen_past + S_new (%lld) exceeds the pool row (%lld)", b, tot,
+                         (long long)L.d.row_stride);
+        T += s_new_host[b];
+        kv_total += tot;
+        n_items += (s_new_host[b] + 2 * TQ - 1) / (2 * TQ);
+    }
+    DKV_REQUIRE(T < (1ll << 30) && kv_total < (1ll << 30), "batch too large");
+    const bool stage = paged || L.pool_on_host;
+    DKV_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+    // ---- metadata: [s_new | past | q_row0 | slot0 | rows | kv_off (B + 1) | pad | items (2 per entry, 8-byte aligned)] ----
+    const size_t items_at = static_cast<size_t>(6) * B + 2;
+    const size_t ints = items_at + 2 * static_cast<size_t>(n_items);
+    int rc = ensure_ragged(ctx, ints);
+    if (rc != DKV_OK) return rc;
+    if (ctx->ragged_pending) {           // the previous upload must have left the host mirror
+        DKV_CUDA(cudaEventSynchronize(ctx->ev_ragged));
+        ctx->ragged_pending = false;
+    }
+    int* hs_new = ctx->ragged_host;
+    int* hpast = hs_new + B;
+    int* hq0 = hpast + B;
+    int* hslot0 = hq0 + B;
+    int* hrows = hslot0 + B;
+    int* hkvoff = hrows + B;
+    int* hitems = ctx->ragged_host + items_at;
+    struct Item { long long key; int b, qt; };
+    std::vector<Item> items;
+    items.reserve(static_cast<size_t>(n_items));
+    int q_acc = 0, kv_acc = 0;
+    for (int b = 0; b < B; ++b) {
+        hs_new[b] = s_new_host[b];
+        hpast[b] = past_host[b];
+        hq0[b] = q_acc;
+        hrows[b] = rows_host[b];
+        hkvoff[b] = kv_acc;
+        hslot0[b] = stage ? kv_acc : static_cast<int>(static_cast<long long>(rows_host[b]) * L.d.row_stride);
+        const int n_qt = (s_new_host[b] + 2 * TQ - 1) / (2 * TQ);
+        for (int qt = 0; qt < n_qt; ++qt) {
+            long long end = is_causal ? static_cast<long long>(past_host[b]) + static_cast<long long>(qt + 1) * 2 * TQ
+                                      : static_cast<long long>(past_host[b]) + s_new_host[b];
+            items.push_back({end, b, qt});
+        }
+        q_acc += s_new_host[b];
+        kv_acc += past_host[b] + s_new_host[b];
+    }
+    hkvoff[B] = kv_acc;
+    std::stable_sort(items.begin(), items.end(), [](const Item& a, const Item& c) { return a.key > c.key; });   // longest first
+    for (size_t i = 0; i < items.size(); ++i) {
+        hitems[2 * i] = items[i].b;
+        hitems[2 * i + 1] = items[i].qt;
+    }
+    DKV_CUDA(cudaMemcpyAsync(ctx->ragged_dev, ctx->ragged_host, ints * sizeof(int), cudaMemcpyHostToDevice, st));
+    DKV_CUDA(cudaEventRecord(ctx->ev_ragged, st));
+    ctx->ragged_pending = true;
+    const int* ds_new = ctx->ragged_dev;
+    const int* dpast = ds_new + B;
+    const int* dq0 = dpast + B;
+    const int* dslot0 = dq0 + B;
+    const int* drows = dslot0 + B;
+    const int* dkvoff = drows + B;
+    const int2* ditems = reinterpret_cast<const int2*>(ctx->ragged_dev + items_at);
+
+    const size_t stage_bytes = stage ? static_cast<size_t>(kv_total) * nh_kv * 256 : 0;
+    ScratchPlan sp = plan_scratch(ctx, T, nh_q, nh_kv, L.d.hidden, project, false, stage_bytes);
+    rc = ensure_scratch(ctx, sp.total);
+    if (rc != DKV_OK) return rc;
+    uint8_t* base = ctx->scratch;
+    if (project) {
+        int* tok_pos = reinterpret_cast<int*>(base + sp.tok_pos);
+        int* tok_slot = reinterpret_cast<int*>(base + sp.tok_slot);
+        extend_prep_ragged_kernel<<<static_cast<int>((T + 255) / 256), 256, 0, st>>>(B, static_cast<int>(T), dq0, dpast, drows,
+                                                                                  L.d.row_stride, tok_pos, tok_slot);
+        DKV_CUDA(cudaGetLastError());
+        ctx->launches += 1;
+        rc = launch_projection(ctx, L, X, static_cast<int>(T), tok_pos, tok_slot, true, nullptr,
+                               reinterpret_cast<float*>(base + sp.splitk), st);
+        if (rc != DKV_OK) return rc;
+    }
+    CUtensorMap tmQ, tmKs, tmVs;
+    rc = encode_tile_map(&tmQ, Q, T, nh_q, G, TQ);
+    if (rc != DKV_OK) return rc;
+    const CUtensorMap* tmK = &L.tmK_128;
+    const CUtensorMap* tmV = &L.tmV_128;
+    if (stage) {
+        uint4* ks = reinterpret_cast<uint4*>(base + sp.stage_k);
+        uint4* vs = reinterpret_cast<uint4*>(base + sp.stage_v);
+        stage_rows_ragged_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(ks, vs, static_cast<const uint4*>(L.k_dev),
+                                                                    static_cast<const uint4*>(L.v_dev), B, dkvoff, drows,
+                                                                    L.d.row_stride, nh_kv * 16, page_table, pt_stride,
+                                                                    L.page_shift);
+        DKV_CUDA(cudaGetLastError());
+        ctx->launches += 1;
+        if ((rc = encode_tile_map(&tmKs, ks, kv_total, nh_kv, 1, kExtTile)) != DKV_OK) return rc;
+        if ((rc = encode_tile_map(&tmVs, vs, kv_total, nh_kv, 1, kExtTile)) != DKV_OK) return rc;
+        tmK = &tmKs;
+        tmV = &tmVs;
+    }
+    ExtendParams ep{};
+    ep.nh_q = nh_q;
+    ep.nh_kv = nh_kv;
+    ep.G = G;
+    ep.g_total = g_total;
+    ep.nsub = nsub;
+    ep.is_causal = is_causal;
+    ep.scale_log2 = softmax_scale * 1.4426950408889634f;
+    ep.out = static_cast<__nv_bfloat16*>(O);
+    ep.status = ctx->status;
+    ep.items = ditems;
+    ep.r_s_new = ds_new;
+    ep.r_past = dpast;
+    ep.r_q_row0 = dq0;
+    ep.r_slot0 = dslot0;
+    dim3 grid(nh_kv * nsub, static_cast<unsigned>(n_items), 1);
+    extend_attn_pp_kernel<<<grid, kPpThreads, kPpSmem, st>>>(tmQ, *tmK, *tmV, ep);
+    DKV_CUDA(cudaGetLastError());
+    ctx->launches += 1;
+    return DKV_OK;
 }
 
 int dkv_scatter_kv(dkv_context* ctx, void* k_pool, void* v_pool, int64_t n_slots, int64_t k_row_bytes,

@@ -39,6 +39,14 @@ struct ExtendParams {
     float scale_log2;
     __nv_bfloat16* out;         // [B, S_new, nh_q, 128]
     unsigned int* status;
+    // Ragged batch (extend_attn_pp_kernel only): blockIdx.y indexes a work list of (request, query-tile pair)
+    // sorted longest first; every request has its own number of new rows, past length, first row in the packed
+    // Q / O tensors and first slot of its K/V rows.  nullptr: uniform batch described by the fields above.
+    const int2* items;
+    const int* r_s_new;
+    const int* r_past;
+    const int* r_q_row0;
+    const int* r_slot0;
     unsigned long long* timing; // optional cycle counters of the ping-pong kernel (builds with DKV_PP_TIMING), else nullptr
     int dbg_mode;               // DKV_PP_TIMING builds: 1 = softmax groups skip their arithmetic, 2 = issuers skip the products
 };

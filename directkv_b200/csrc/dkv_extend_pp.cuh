@@ -73,14 +73,26 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     PP_DECL;
     const int G = p.G, TQ = kExtTile / G;
-    const int qt = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);   // longest (latest) tiles first
-    const int b = blockIdx.z;
     const int h = blockIdx.x / p.nsub, sub = blockIdx.x % p.nsub;
     const int qhead0 = h * p.g_total + sub * G;
-    const int past = p.n_past_blocks ? p.n_past_blocks[0] * 64 : p.seqlen_past;
+    int qt, s_new, past, q_row0, row_slot0;
+    if (p.items != nullptr) {                                 // ragged batch: the host sorted the work list
+        const int2 it = p.items[blockIdx.y];
+        qt = it.y;
+        s_new = p.r_s_new[it.x];
+        past = p.r_past[it.x];
+        q_row0 = p.r_q_row0[it.x];
+        row_slot0 = p.r_slot0[it.x];
+    } else {
+        const int b = blockIdx.z;
+        qt = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);   // longest (latest) tiles first
+        s_new = p.S_new;
+        past = p.n_past_blocks ? p.n_past_blocks[0] * 64 : p.seqlen_past;
+        q_row0 = b * p.S_new;
+        row_slot0 = static_cast<int>(static_cast<long long>(p.vrow ? p.vrow[b] : b) * p.row_stride);
+    }
     const int q0 = qt * 2 * TQ;                               // first new token of tile 0; tile 1 starts at q0 + TQ
-    const int row_slot0 = static_cast<int>(static_cast<long long>(p.vrow ? p.vrow[b] : b) * p.row_stride);
-    const int s_total = past + p.S_new;
+    const int s_total = past + s_new;
     int n_half[2];                                            // half-tiles of 64 keys each group walks
 #pragma unroll
     for (int g = 0; g < 2; ++g) {
@@ -125,8 +137,8 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
                 // Rows r = t * G + head come as a (d, head, token) box: G heads of TQ tokens.
-                tma_load_3d(sQ + g * kExtTileBytes, &tmQ, &ctl->bar_q, 0, qhead0, b * p.S_new + q0 + g * TQ);
-                tma_load_3d(sQ + g * kExtTileBytes + kExtHalfBytes, &tmQ, &ctl->bar_q, 64, qhead0, b * p.S_new + q0 + g * TQ);
+                tma_load_3d(sQ + g * kExtTileBytes, &tmQ, &ctl->bar_q, 0, qhead0, q_row0 + q0 + g * TQ);
+                tma_load_3d(sQ + g * kExtTileBytes + kExtHalfBytes, &tmQ, &ctl->bar_q, 64, qhead0, q_row0 + q0 + g * TQ);
             }
             for (int q = 0; q < 2 * n_max; ++q) {             // q even: K(q/2), odd: V(q/2)
                 if (PP_MODE(4)) break;
@@ -373,8 +385,8 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             ctl->abort = 1;
         } else {
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            const bool store = my_tok < p.S_new;
-            __nv_bfloat16* dst = p.out + ((static_cast<long long>(b) * p.S_new + (store ? my_tok : 0)) * p.nh_q + qhead0 + row % G) * 128;
+            const bool store = my_tok < s_new;
+            __nv_bfloat16* dst = p.out + ((static_cast<long long>(q_row0) + (store ? my_tok : 0)) * p.nh_q + qhead0 + row % G) * 128;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];

@@ -343,19 +343,19 @@ class DirectKVBackend(AttentionBackend):
         ext, pre = meta.extend_seq_lens_cpu, meta.extend_prefix_lens_cpu
         if x_all is None or lid not in self._registered or ext is None:
             return self._extend_token_pool(q, k, v, layer, forward_batch)
-        out = torch.empty(q.shape[0], nh_q * d, dtype=q.dtype, device=q.device)
-        off = 0
-        for i in range(bs):
-            n_new = int(ext[i])
-            n_pre = int(pre[i]) if pre else 0
-            if n_new == 0:
-                continue
-            x_i = x_all[off:off + n_new].reshape(1, n_new, self.hidden_size).contiguous()
-            q_i = q[off:off + n_new].reshape(1, n_new, nh_q, d).contiguous()
-            o_i = kernel.extend(lid, x_i, q_i, float(layer.scaling), True, n_pre, -1, row_map=meta.rows_dev[i:i + 1])
-            out[off:off + n_new] = o_i.view(n_new, nh_q * d)
-            off += n_new
-        return out
+        # One launch sequence for the whole ragged batch (the reference calls its kernel once per request,
+        # directkv/directkv_backend.py:681-697); requests without new rows take no part.
+        live = [i for i in range(bs) if int(ext[i]) > 0]
+        n_rows = sum(int(ext[i]) for i in live)
+        if not live:
+            return q.new_zeros(q.shape[0], nh_q * d)
+        if n_rows != q.shape[0]:
+            raise ValueError(f"{self._NAME}: extend_seq_lens sum to {n_rows} rows but q has {q.shape[0]}")
+        out = kernel.extend_ragged(
+            lid, x_all.reshape(n_rows, self.hidden_size).contiguous(), q.reshape(n_rows, nh_q, d).contiguous(),
+            [int(ext[i]) for i in live], [int(pre[i]) if pre else 0 for i in live],
+            [self._pool.row_of(meta.req_pool_indices_cpu[i]) for i in live], float(layer.scaling), True)
+        return out.view(n_rows, nh_q * d)
 
     def _extend_token_pool(self, q, k, v, layer, forward_batch) -> torch.Tensor:
         """Data flow of ``_sdpa_extend_manual`` (:861-891) on the engine: store k, v, then every new row
@@ -374,19 +374,30 @@ class DirectKVBackend(AttentionBackend):
         # (its rows are gathered through req_to_token once); shorter ones are batched as one virtual decode
         # request per new row.
         vlen, vrow, vidx = [], [], []
+        long_req, long_idx = [], []
         off = 0
         for i in range(bs):
             n_new, n_pre = int(ext[i]), int(pre[i])
             if n_new * g_total >= 128:
-                q_i = q[off:off + n_new].reshape(1, n_new, nh_q, d).contiguous()
-                o_i = kernel.extend_attend(eng, q_i, float(layer.scaling), True, n_pre,
-                                           row_map=meta.req_idx_dev[i:i + 1], page_table=table)
-                out[off:off + n_new] = o_i.view(n_new, nh_q * d)
+                long_req.append((n_new, n_pre, meta.req_pool_indices_cpu[i]))
+                long_idx.append((off, n_new))
             else:
                 vlen += [n_pre + j + 1 for j in range(n_new)]
                 vrow += [meta.req_pool_indices_cpu[i]] * n_new
                 vidx += list(range(off, off + n_new))
             off += n_new
+        if long_req:
+            whole = len(long_req) == bs
+            q_long = q if whole else torch.cat([q[o:o + n] for o, n in long_idx])
+            o_long = kernel.extend_ragged(eng, None, q_long.reshape(-1, nh_q, d).contiguous(), [r[0] for r in long_req],
+                                          [r[1] for r in long_req], [r[2] for r in long_req], float(layer.scaling), True,
+                                          page_table=table).view(-1, nh_q * d)
+            if whole:
+                return o_long
+            pos = 0
+            for o, n in long_idx:
+                out[o:o + n] = o_long[pos:pos + n]
+                pos += n
         if vlen:
             vlen_t = torch.tensor(vlen, dtype=torch.int32).to(self.device, non_blocking=True)
             vrow_t = torch.tensor(vrow, dtype=torch.int32).to(self.device, non_blocking=True)

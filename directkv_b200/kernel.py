@@ -10,7 +10,7 @@ torch compute and no fallback.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -240,6 +240,48 @@ def extend_attend(
     _lib.check(_lib.load().dkv_extend_attend(
         ctx.handle, int(layer_id), _ptr(Q), _ptr(out), B, S_new, Q.size(2), float(softmax_scale),
         1 if is_causal else 0, int(seqlen_past), _ptr(row_map), _ptr(page_table), int(pt_stride), _stream()))
+    return out
+
+
+def extend_ragged(
+    layer_id: int,
+    X: Optional[torch.Tensor],        # [T, H] bf16 CUDA, or None when the new rows are stored already
+    Q: torch.Tensor,                  # [T, NH_q, 128] bf16 CUDA: the requests' rows one after the other
+    s_new: Sequence[int],             # new rows per request (host)
+    past: Sequence[int],              # stored rows per request (host)
+    rows: Sequence[int],              # pool row / page-table row per request (host)
+    softmax_scale: float,
+    is_causal: bool = True,
+    page_table: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Extend of a ragged batch in one launch sequence (``dkv_extend_ragged``); the reference calls its kernel
+    once per request (directkv/directkv_backend.py:681-697)."""
+    import ctypes as C
+
+    _check_cuda_bf16(Q, "Q")
+    _chk(Q.dim() == 3 and Q.size(2) == HEAD_DIM, "Q must be [T,NH_q,128]")
+    B = len(s_new)
+    _chk(len(past) == B and len(rows) == B and B > 0, "s_new, past and rows must have one entry per request")
+    _chk(int(sum(int(n) for n in s_new)) == Q.size(0), "sum(s_new) must equal the rows of Q")
+    if X is not None:
+        _check_cuda_bf16(X, "X")
+        _chk(X.dim() == 2 and X.size(0) == Q.size(0), "X must be [T,H]")
+    pt_stride = 0
+    if page_table is not None:
+        _chk(page_table.is_cuda and page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1,
+             "page_table must be a 2-D int32 CUDA tensor with unit inner stride")
+        pt_stride = page_table.stride(0)
+    if out is None:
+        out = torch.empty_like(Q)
+    _check_cuda_bf16(out, "out")
+    arr = C.c_int32 * B
+    a_new, a_past, a_rows = arr(*[int(v) for v in s_new]), arr(*[int(v) for v in past]), arr(*[int(v) for v in rows])
+    ctx = get_context(Q.device.index)
+    _lib.check(_lib.load().dkv_extend_ragged(
+        ctx.handle, int(layer_id), _ptr(X), _ptr(Q), _ptr(out), B, C.cast(a_new, C.c_void_p), C.cast(a_past, C.c_void_p),
+        C.cast(a_rows, C.c_void_p), Q.size(1), float(softmax_scale), 1 if is_causal else 0, _ptr(page_table),
+        int(pt_stride), _stream()))
     return out
 
 

@@ -227,6 +227,18 @@ int dkv_extend_attend(dkv_context* ctx, int layer_id, const void* Q, void* O, in
                       const int32_t* page_table, int64_t pt_stride, void* stream);
 
 /*
+ * Extend of a RAGGED batch in one launch sequence: request b has s_new[b] new rows on past[b] stored rows and
+ * uses pool row (or page-table row) rows[b]; the three arrays are HOST memory ([B] int32).  X [T, H] (or NULL:
+ * the rows are in the pool already) and Q / O [T, nh_q, 128] hold the requests' rows one after the other,
+ * T = sum of s_new.  The reference loops over the requests with one kernel call each
+ * (directkv/directkv_backend.py:681-697); here the (request, query tile) pairs of the whole batch form one work
+ * list, longest first, for one launch of the extend kernel.  Not capturable in a CUDA graph (host-side lengths).
+ */
+int dkv_extend_ragged(dkv_context* ctx, int layer_id, const void* X, const void* Q, void* O, int B,
+                      const int32_t* s_new_host, const int32_t* past_host, const int32_t* rows_host, int nh_q,
+                      float softmax_scale, int is_causal, const int32_t* page_table, int64_t pt_stride, void* stream);
+
+/*
  * Stream-ordered store of new tokens into a token-indexed pool: replaces the blocking
  * device-to-host copy plus CPU scatter of DirectKVTokenToKVPool.set_kv_buffer
  * (directkv/directkv_pool.py:174-209).  Row i of cache_k / cache_v ([n_tokens, row_bytes],

@@ -256,6 +256,69 @@ def test_extend_attend_contiguous_rows_and_errors():
         kernel.extend_attend(72, Q.to(DEV), SCALE, True, 0)
 
 
+@pytest.mark.parametrize("host", [True, False])
+def test_extend_ragged_batch(host):
+    """Three requests with different new / past lengths in ONE launch sequence (projection + RoPE + write-back +
+    attention), each compared with the oracle run on that request alone; rows of the pool that no request writes
+    stay bit-identical."""
+    nh_q, nh_kv, H, s_pad = 8, 2, 256, 640
+    s_new, past, rows = [200, 70, 333], [0, 130, 64], [3, 0, 2]
+    g = torch.Generator().manual_seed(4321)
+    Wk = (torch.randn(nh_kv, 128, H, generator=g) * 0.05).to(torch.bfloat16)
+    Wv = (torch.randn(nh_kv, 128, H, generator=g) * 0.05).to(torch.bfloat16)
+    K = (torch.randn(4, s_pad, nh_kv, 128, generator=g) * 0.4).to(torch.bfloat16)
+    V = (torch.randn(4, s_pad, nh_kv, 128, generator=g) * 0.4).to(torch.bfloat16)
+    T = sum(s_new)
+    X = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    Q = torch.randn(T, nh_q, 128, generator=g).to(torch.bfloat16)
+    cs = orc.build_cos_sin(s_pad, 128, 10000.0)
+    Kd, Vd = (K.clone().pin_memory(), V.clone().pin_memory()) if host else (K.to(DEV), V.to(DEV))
+    kernel.register_layer(73, Kd, Vd, Wk.to(DEV), Wv.to(DEV), cs.to(DEV), row_stride=s_pad)
+    out = kernel.extend_ragged(73, X.to(DEV), Q.to(DEV), s_new, past, rows, SCALE, True)
+    get_context(0).raise_on_status()
+    Kc, Vc = Kd.cpu(), Vd.cpu()
+    off = 0
+    for n, p, r in zip(s_new, past, rows):
+        kb, vb = K[r:r + 1, :p + n].clone(), V[r:r + 1, :p + n].clone()
+        ref = orc.smpv2_fwd(X[off:off + n].unsqueeze(0), Wk, Wv, Q[off:off + n].unsqueeze(0), kb, vb, cs, SCALE, True, p)
+        assert_close(out[off:off + n], ref[0], f"O of the request in row {r}")
+        assert_close(Kc[r, p:p + n], kb[0, p:], "K write-back", atol=KV_ATOL, rtol=1e-2)
+        assert_close(Vc[r, p:p + n], vb[0, p:], "V write-back", atol=KV_ATOL, rtol=1e-2)
+        assert torch.equal(Kc[r, :p], K[r, :p]) and torch.equal(Kc[r, p + n:], K[r, p + n:])
+        off += n
+    assert torch.equal(Kc[1], K[1]) and torch.equal(Vc[1], V[1])
+    kernel.unregister_layer(73)
+
+
+def test_extend_ragged_attend_paged():
+    """Rows already stored in a token pool (page size 1): ragged attention through the page table."""
+    nh_q, nh_kv = 8, 2
+    s_new, past, rows = [150, 40, 260], [90, 0, 10], [1, 3, 0]
+    g = torch.Generator().manual_seed(99)
+    n_slots = 1200
+    k_pool = (torch.randn(n_slots, nh_kv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    v_pool = (torch.randn(n_slots, nh_kv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    perm = (torch.randperm(n_slots - 1, generator=g) + 1).int()
+    table = torch.zeros(4, 300, dtype=torch.int32)
+    at = 0
+    for n, p, r in zip(s_new, past, rows):
+        table[r, :n + p] = perm[at:at + n + p]
+        at += n + p
+    Q = torch.randn(sum(s_new), nh_q, 128, generator=g).to(torch.bfloat16)
+    kernel.register_layer(74, k_pool.pin_memory(), v_pool.pin_memory(), page_size=1)
+    out = kernel.extend_ragged(74, None, Q.to(DEV), s_new, past, rows, SCALE, True, page_table=table.to(DEV))
+    get_context(0).raise_on_status()
+    off = 0
+    for n, p, r in zip(s_new, past, rows):
+        slots = table[r, :n + p].long()
+        ref = orc.sdpa_extend(Q[off:off + n], k_pool[slots], v_pool[slots], p, SCALE)
+        assert_close(out[off:off + n], ref, f"request in table row {r}")
+        off += n
+    kernel.unregister_layer(74)
+    with pytest.raises(RuntimeError, match="sum"):
+        kernel.extend_ragged(74, None, Q.to(DEV), [1], [0], [0], SCALE)
+
+
 def test_extend_paths_agree():
     """The tensor-core extend kernel and the row-streamed path (decode kernels, one virtual request per new
     row) implement the same function: compare them directly, non-causal included."""
