@@ -49,9 +49,11 @@ METRIC = "decode_attention_kv_gbps"
 UNIT = "GB/s"
 
 
-def c2_lengths(rank: int = 0):
+def c2_lengths():
+    """Request lengths of the batch.  Every rank gets the same ones: under head sharding all ranks serve the same
+    requests (each its own KV heads), so the per-GPU work is identical; contents and page placement differ."""
     # +1: the token decoded in this step (its K/V are projected, stored and attended too)
-    return [n + 1 for n in workloads.ragged_lengths_uniform(16, 512, 8192, seed=4234 + CFG_ID + 97 * rank)]
+    return [n + 1 for n in workloads.ragged_lengths_uniform(16, 512, 8192, seed=4234 + CFG_ID)]
 
 
 def measured_peaks():
@@ -138,7 +140,7 @@ def cpu_reference_time(steps: int, warmup: int, lens, sample_idx):
 def run_reference(args, rank):
     if rank != 0:
         return
-    lens = c2_lengths(0)
+    lens = c2_lengths()
     steps = max(1, min(args.steps, 10))
     gbs, ms, cores, sample = cpu_reference_time(steps, max(1, min(args.warmup, 2)), lens, list(range(0, 16, 4)))
     line = {
@@ -360,7 +362,7 @@ def run_sweep(args, rank, world, local_rank, dev, dist):
         if name == "C1":
             one_layer("C1 llama3-8b B=1 ctx 4096", workloads.LLAMA3_8B, [4097], 0, iters=100)
         elif name == "C2":
-            one_layer("C2 opt-6.7b 16 ragged U[512,8192]", workloads.OPT_6_7B, c2_lengths(0), CFG_ID, iters=100)
+            one_layer("C2 opt-6.7b 16 ragged U[512,8192]", workloads.OPT_6_7B, c2_lengths(), CFG_ID, iters=100)
         elif name.startswith("C3"):
             for n in (32768, 131072, 524288, 1048576):
                 if world > 1 and n < 1048576:
@@ -452,7 +454,7 @@ def main():
         return
 
     shape = workloads.OPT_6_7B
-    lens = c2_lengths(rank)
+    lens = c2_lengths()
     ctx = get_context(local_rank)
     if args.variant is not None:
         ctx.set("attn_variant", args.variant)
