@@ -145,7 +145,7 @@ struct dkv_context {
     int proj_split_k = 0;
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
     int proj_wide = 1;                  // 256-token projection tiles when there are more 128-token tiles than SMs
-    int proj_decode = -1;               // -1: swapped-operand projection kernel when T <= 128; 0 never; 1 same as -1
+    int proj_decode = -1;               // swapped-operand projection kernel: -1 when it can run under the streaming kernel; 0 never; 1 whenever T <= 512
     int attn_mma = -1;                  // -1: tensor-core inner product when 3..16 query heads share a KV head; 0 never; 1 always
     int extend_pingpong = 1;            // two query tiles per CTA with specialised warps (0: one tile, four warps)
     int extend_rowwise = 0;             // 1: extend attends row by row with the decode kernels (reference path for tests)
@@ -464,13 +464,14 @@ void proj_split(const dkv_context* ctx, int T, int nh_kv, int H, int* split_k, i
 
 // Split of the hidden dimension for the decode-batch projection: one CTA per (KV head, slice), about one
 // CTA per SM, at least four 64-column chunks per slice.
-void proj_decode_split(const dkv_context* ctx, int nh_kv, int H, int* split_k, int* cps) {
+void proj_decode_split(const dkv_context* ctx, int T, int nh_kv, int H, int* split_k, int* cps) {
     const int nchunks = H / kProjBK;
-    int s = ctx->proj_split_k > 0 ? ctx->proj_split_k : ctx->sm_count / (nh_kv > 0 ? nh_kv : 1);
+    const int units = nh_kv * ((T + kPdMaxTokens - 1) / kPdMaxTokens);       // (KV head, 128-token chunk) pairs
+    int s = ctx->proj_split_k > 0 ? ctx->proj_split_k : ctx->sm_count / (units > 0 ? units : 1);
     if (ctx->proj_split_k <= 0 && s > nchunks / 4) s = nchunks / 4;
     if (s < 1) s = 1;
     if (s > nchunks) s = nchunks;
-    if (nh_kv > kMaxCounters) s = 1;
+    if (units > kMaxCounters) s = 1;
     const int c = (nchunks + s - 1) / s;
     *cps = c;
     *split_k = (nchunks + c - 1) / c;
@@ -508,11 +509,16 @@ ScratchPlan plan_scratch(const dkv_context* ctx, int64_t rows, int nh_q, int nh_
         }
         // The decode-batch kernel (up to 128 rows) splits differently; a plan made for many rows also covers
         // a later call with few.
-        proj_decode_split(ctx, nh_kv, hidden, &split_k, &cps);
-        if (split_k > 1) {
-            const size_t n_pad = pd_padded_tokens(static_cast<int>(rows < kPdMaxTokens ? rows : kPdMaxTokens));
-            const size_t dec = static_cast<size_t>(split_k) * nh_kv * 2 * n_pad * kProjHead * 4;
-            bytes = bytes > dec ? bytes : dec;
+        // Worst case over the batches a later call may bring: one token chunk with the deepest split, or all chunks.
+        for (int64_t t : {static_cast<int64_t>(rows < kPdMaxTokens ? rows : kPdMaxTokens),
+                          static_cast<int64_t>(rows < kPdMaxBatch ? rows : kPdMaxBatch)}) {
+            proj_decode_split(ctx, static_cast<int>(t), nh_kv, hidden, &split_k, &cps);
+            if (split_k > 1) {
+                const size_t box_rows = t > kPdMaxTokens ? kPdMaxTokens : pd_padded_tokens(static_cast<int>(t));
+                const size_t n_chunks = (t + kPdMaxTokens - 1) / kPdMaxTokens;
+                const size_t dec = static_cast<size_t>(split_k) * nh_kv * n_chunks * 2 * box_rows * kProjHead * 4;
+                bytes = bytes > dec ? bytes : dec;
+            }
         }
         off += align256(bytes);
     }
@@ -604,20 +610,24 @@ unsigned long long* pp_timing_buffer() {
 
 // Projection of T rows of X with RoPE and write-back (tcgen05 kernel).
 int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int T, const int* tok_pos,
-                      const int* tok_slot, bool store_pool, __nv_bfloat16* kv_new, float* splitk, cudaStream_t st) {
-    const bool small = T <= kPdMaxTokens && ctx->proj_decode != 0;
+                      const int* tok_slot, bool store_pool, __nv_bfloat16* kv_new, float* splitk, cudaStream_t st,
+                      bool beside_streaming = false) {
+    // The swapped-operand kernel pays off where it runs UNDER the streaming kernel (the 16-warp CUDA-core form
+    // leaves it registers and shared memory); alone, the 128-token-tile kernel with its deeper ring is faster.
+    const bool small = T <= kPdMaxBatch && (ctx->proj_decode == 1 || (ctx->proj_decode < 0 && beside_streaming));
     ProjParams pp{};
     pp.T = T;
     pp.H = L.d.hidden;
     pp.nh_kv = L.d.nh_kv;
-    if (small) proj_decode_split(ctx, L.d.nh_kv, L.d.hidden, &pp.split_k, &pp.chunks_per_split);
+    if (small) proj_decode_split(ctx, T, L.d.nh_kv, L.d.hidden, &pp.split_k, &pp.chunks_per_split);
     else proj_split(ctx, T, L.d.nh_kv, L.d.hidden, &pp.split_k, &pp.chunks_per_split);
     // More 128-token tiles than SMs (prefill sizes): 256 tokens per CTA, so the weights cross L2 once per 256.
     const int tiles128 = (T + kProjBM - 1) / kProjBM;
     const bool wide = !small && pp.split_k == 1 && ctx->proj_wide != 0 &&
                       static_cast<long long>(tiles128) * L.d.nh_kv > ctx->sm_count;
     CUtensorMap tmX;
-    int rc = encode_operand_map(&tmX, x, T, L.d.hidden, small ? pd_padded_tokens(T) : wide ? 256 : 128);
+    const int pd_box_rows = T > kPdMaxTokens ? kPdMaxTokens : pd_padded_tokens(T);
+    int rc = encode_operand_map(&tmX, x, T, L.d.hidden, small ? pd_box_rows : wide ? 256 : 128);
     if (rc != DKV_OK) return rc;
     pp.tok_pos = tok_pos;
     pp.tok_slot = tok_slot;
@@ -631,8 +641,8 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
     pp.tile_counters = ctx->counters;
     pp.status = ctx->status;
     if (small) {
-        dim3 grid(L.d.nh_kv, pp.split_k);
-        proj_rope_decode_kernel<<<grid, 128, pd_smem_bytes(pd_padded_tokens(T)), st>>>(tmX, L.tmWk, L.tmWv, pp);
+        dim3 grid(L.d.nh_kv, pp.split_k, (T + kPdMaxTokens - 1) / kPdMaxTokens);
+        proj_rope_decode_kernel<<<grid, 128, pd_smem_bytes(pd_box_rows), st>>>(tmX, L.tmWk, L.tmWv, pp);
     } else if (wide) {
         dim3 grid(L.d.nh_kv, (tiles128 + 1) / 2, 1);
         proj_rope_kernel<kProjStagesWide, 2><<<grid, 128, kProjSmem, st>>>(tmX, L.tmWk, L.tmWv, pp);
@@ -929,8 +939,11 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
         // stream (forked after prep, joined before the merge) so the two overlap.
         DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
         DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+        const int g_total = a->nh_q / nh_kv;
+        const bool beside = a->batch > 0 && !use_mma(ctx, g_total, L.pool_on_host) && choose_g(ctx, g_total, L.pool_on_host) == 1 &&
+                            effective_variant(ctx, 1) == 2;
         rc = launch_projection(ctx, L, a->x, a->batch, tok_pos, tok_slot, a->save_kv_cache != 0, kv_new,
-                               reinterpret_cast<float*>(base + sp.splitk), ctx->side);
+                               reinterpret_cast<float*>(base + sp.splitk), ctx->side, beside);
         if (rc != DKV_OK) return rc;
         DKV_CUDA(cudaEventRecord(ctx->ev_join, ctx->side));
     } else if (a->new_mode == DKV_NEW_GIVEN) {

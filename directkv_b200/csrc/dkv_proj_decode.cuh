@@ -21,7 +21,8 @@ namespace dkv {
 
 constexpr int kPdStages    = 2;
 constexpr int kPdWBytes    = kProjHead * kProjBK * 2;   // 16 KB: one 64-column chunk of Wk_h or Wv_h
-constexpr int kPdMaxTokens = 128;
+constexpr int kPdMaxTokens = 128;                       // tokens per CTA (N side of the product)
+constexpr int kPdMaxBatch  = 512;                       // larger batches use the 128-token-tile kernel
 constexpr int kPdChunkTok  = 32;                        // tokens per epilogue pass
 constexpr int kPdAccStride = 132;                       // floats between token rows of the fp32 epilogue tile
 constexpr int kPdCtrlBytes = 256;
@@ -34,14 +35,18 @@ __host__ __device__ constexpr size_t pd_smem_bytes(int n_pad) {
 static_assert(2 * kPdChunkTok * kPdAccStride * 4 + kPdChunkTok * 512 <= kPdStages * pd_stage_bytes(16),
               "epilogue tiles must fit in the operand ring");
 
-// grid (nh_kv, split_k), 128 threads.  tmX has box {64, n_pad}; tmWk/tmWv box {64, 128}.
+// grid (nh_kv, split_k, ceil(T / 128)), 128 threads: a CTA owns one KV head, one slice of the hidden dimension and
+// up to 128 tokens.  tmX has box {64, min(128, T padded to 16)}; tmWk/tmWv box {64, 128}.
 __global__ void __launch_bounds__(128, 5)   // at most 96 registers: the CTA must fit beside a streaming CTA
 proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmWk,
                         const __grid_constant__ CUtensorMap tmWv, const ProjParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    const int n_pad = pd_padded_tokens(p.T);
-    const int stage_bytes = pd_stage_bytes(n_pad);
+    const int tok_base = static_cast<int>(blockIdx.z) * kPdMaxTokens;
+    const int T_cta = (p.T - tok_base) < kPdMaxTokens ? (p.T - tok_base) : kPdMaxTokens;   // tokens of this CTA
+    const int n_pad = pd_padded_tokens(T_cta);                         // N of the product
+    const int box_rows = p.T > kPdMaxTokens ? kPdMaxTokens : pd_padded_tokens(p.T);        // rows one TMA box of X brings
+    const int stage_bytes = pd_stage_bytes(box_rows);
     const int vcol = n_pad <= 64 ? 64 : 128;             // TMEM column of the V accumulator
     const uint32_t tmem_cols = 2u * vcol;
     uint8_t* ctrl = smem + kPdStages * stage_bytes;
@@ -97,7 +102,7 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
                 const int kc = (c0 + i) * kProjBK;
                 tma_load_2d(st, &tmWk, &full_bar[s], kc, h * kProjHead);
                 tma_load_2d(st + kPdWBytes, &tmWv, &full_bar[s], kc, h * kProjHead);
-                tma_load_2d(st + 2 * kPdWBytes, &tmX, &full_bar[s], kc, 0);
+                tma_load_2d(st + 2 * kPdWBytes, &tmX, &full_bar[s], kc, tok_base);   // rows past T read as zeros
             }
         }
         __syncwarp();
@@ -143,12 +148,14 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
     __syncthreads();
     const bool aborted = (flags[0] != 0);  // uniform across the CTA
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-    const int npass = (p.T + kPdChunkTok - 1) / kPdChunkTok;
-    const size_t slice_floats = static_cast<size_t>(2) * n_pad * kProjHead;   // one (split, head) slice: [2][n_pad][128]
+    const int npass = (T_cta + kPdChunkTok - 1) / kPdChunkTok;
+    const int n_chunks = static_cast<int>(gridDim.z);
+    const int unit = h * n_chunks + static_cast<int>(blockIdx.z);              // (head, token chunk) of this CTA
+    const size_t slice_floats = static_cast<size_t>(2) * box_rows * kProjHead; // one (split, unit) slice: [2][box_rows][128]
     bool finalize = !aborted;
 
     if (!aborted && p.split_k > 1) {
-        float* mine = p.splitk_scratch + (static_cast<size_t>(sp) * p.nh_kv + h) * slice_floats + tid;
+        float* mine = p.splitk_scratch + (static_cast<size_t>(sp) * p.nh_kv * n_chunks + unit) * slice_floats + tid;
 #pragma unroll 1
         for (int c = 0; c < npass; ++c) {
 #pragma unroll 1
@@ -159,16 +166,16 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
                     const int tok = c * kPdChunkTok + i;
-                    if (tok < p.T) mine[(static_cast<size_t>(kv) * n_pad + tok) * kProjHead] = __uint_as_float(r[i]);
+                    if (tok < T_cta) mine[(static_cast<size_t>(kv) * box_rows + tok) * kProjHead] = __uint_as_float(r[i]);
                 }
             }
         }
         __threadfence();
         __syncthreads();
         if (tid == 0) {
-            const unsigned int prev = atomicAdd(&p.tile_counters[h], 1u);
+            const unsigned int prev = atomicAdd(&p.tile_counters[unit], 1u);
             const int last = (prev == static_cast<unsigned int>(p.split_k - 1));
-            if (last) p.tile_counters[h] = 0u;  // ready for the next launch
+            if (last) p.tile_counters[unit] = 0u;  // ready for the next launch
             flags[1] = last;
         }
         __syncthreads();
@@ -182,7 +189,7 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
 #pragma unroll 1
         for (int c = 0; c < npass; ++c) {
             const int tok0 = c * kPdChunkTok;
-            const int rows = (p.T - tok0) < kPdChunkTok ? (p.T - tok0) : kPdChunkTok;
+            const int rows = (T_cta - tok0) < kPdChunkTok ? (T_cta - tok0) : kPdChunkTok;
             if (p.split_k == 1) {
 #pragma unroll 1
                 for (int kv = 0; kv < 2; ++kv) {
@@ -193,11 +200,11 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
                     for (int i = 0; i < 32; ++i) sacc[(kv * kPdChunkTok + i) * kPdAccStride + tid] = __uint_as_float(r[i]);
                 }
             } else {
-                const float* slice0 = p.splitk_scratch + static_cast<size_t>(h) * slice_floats;
-                const size_t split_stride = static_cast<size_t>(p.nh_kv) * slice_floats;
+                const float* slice0 = p.splitk_scratch + static_cast<size_t>(unit) * slice_floats;
+                const size_t split_stride = static_cast<size_t>(p.nh_kv) * n_chunks * slice_floats;
                 for (int idx = tid; idx < 2 * rows * 32; idx += 128) {
                     const int c4 = idx & 31, r = (idx >> 5) % rows, kv = (idx >> 5) / rows;
-                    const float* src = slice0 + (static_cast<size_t>(kv) * n_pad + tok0 + r) * kProjHead + c4 * 4;
+                    const float* src = slice0 + (static_cast<size_t>(kv) * box_rows + tok0 + r) * kProjHead + c4 * 4;
                     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int s2 = 0; s2 < p.split_k; ++s2) {
                         const float4 f = __ldcg(reinterpret_cast<const float4*>(src + s2 * split_stride));
@@ -212,7 +219,7 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
             __syncthreads();
             // Round, rotate K (dims d and d + 64 together), round again; V is rounded once.
             for (int r = 0; r < rows; ++r) {
-                const int tok = tok0 + r;
+                const int tok = tok_base + tok0 + r;       // row of X / position in the batch
                 if (tid < 64) {
                     float lo = round_bf16(sacc[r * kPdAccStride + tid]);
                     float hi = round_bf16(sacc[r * kPdAccStride + tid + 64]);
@@ -239,7 +246,7 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
             __syncthreads();
             // Coalesced copy-out: one warp writes one token's 256-byte K row and 256-byte V row.
             for (int r = warp; r < rows; r += 4) {
-                const int tok = tok0 + r;
+                const int tok = tok_base + tok0 + r;       // row of X / position in the batch
                 const uint4 w = *reinterpret_cast<const uint4*>(stage_out + r * 512 + lane * 16);
                 if (p.kv_new != nullptr)
                     *reinterpret_cast<uint4*>(p.kv_new + (static_cast<size_t>(tok) * p.nh_kv + h) * 256 + lane * 8) = w;

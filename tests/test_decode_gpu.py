@@ -91,19 +91,26 @@ def test_forms_of_the_streaming_kernel_agree():
     assert (a.float() - b.float()).abs().max().item() < 1e-2
 
 
-@pytest.mark.parametrize("batch", [1, 15, 16, 17, 33, 64, 65, 128, 129])
+@pytest.mark.parametrize("batch", [1, 15, 16, 17, 33, 64, 65, 128, 129, 257, 512, 513])
 @pytest.mark.parametrize("hidden", [64, 320, 4096])
 def test_projection_batch_sizes(batch, hidden):
-    """Decode batches on both projection kernels: up to 128 tokens the swapped-operand kernel (tokens on the
-    N side, 16..128 padded columns, split-K by KV head), above that the 128-token-tile kernel."""
+    """Decode batches on both projection kernels: up to 512 tokens the swapped-operand kernel (tokens on the
+    N side in chunks of up to 128, 16..128 padded columns, split-K per KV head and chunk), above that the
+    128-token-tile kernel."""
     lens = [1 + (7 * i) % 40 for i in range(batch)]
-    _run_decode(_shape(hidden, 4, 2), lens, 16, cfg_id=20 + batch)
+    ctx = get_context(0)
+    for flag in (1, 0):                      # 1: swapped-operand kernel whenever the batch fits; 0: never
+        ctx.set("proj_decode", flag)
+        try:
+            _run_decode(_shape(hidden, 4, 2), lens, 16, cfg_id=20 + batch)
+        finally:
+            ctx.set("proj_decode", -1)
 
 
 def test_projection_kernels_agree():
     ctx = get_context(0)
     outs = []
-    for flag in (0, -1):
+    for flag in (0, 1):
         ctx.set("proj_decode", flag)
         outs.append(_run_decode(_shape(1024, 8, 4), [30, 1, 17, 64, 5], 16, cfg_id=77))
     ctx.set("proj_decode", -1)
