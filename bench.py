@@ -235,6 +235,40 @@ def measure_extend(dev, steps, warmup):
             "attention_tflops": attn_flops / med / 1e9, "attention_plus_projection_tflops": (attn_flops + proj_flops) / med / 1e9}
 
 
+def measure_request_pool(dev, lens, steps=5, warmup=2):
+    """The same batch in the request pool's layout (one contiguous pinned row per request,
+    directkv/directkv_request_pool.py:66-76): past rows streamed by the SMs against brought in by the copy
+    engines (directkv_b200/staging.py).  GB/s of KV per step, host->device copies inside the timed region."""
+    from directkv_b200 import kernel
+    from directkv_b200._lib import get_context
+    from directkv_b200.staging import DmaStagedDecode
+
+    shape = workloads.OPT_6_7B
+    B, s_pad = len(lens), (max(lens) + 63) // 64 * 64
+    g = torch.Generator().manual_seed(4321)
+    k = torch.empty(B, s_pad, shape.nh_kv, 128, dtype=torch.bfloat16).normal_(0, 0.5, generator=g).pin_memory()
+    v = torch.empty_like(k).normal_(0, 0.5, generator=g).pin_memory()
+    wk = (torch.randn(shape.nh_kv, 128, shape.hidden, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+    wv = (torch.randn(shape.nh_kv, 128, shape.hidden, generator=g) * 0.02).to(torch.bfloat16).to(dev)
+    q = torch.randn(B, shape.nh_q * 128, generator=g).to(torch.bfloat16).to(dev)
+    x = torch.randn(B, shape.hidden, generator=g).to(torch.bfloat16).to(dev)
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    rm = torch.arange(B, dtype=torch.int32, device=dev)
+    out = torch.empty_like(q)
+    layer = 77
+    kernel.register_layer(layer, k, v, wk, wv, None, row_stride=s_pad, device=dev.index)
+    stager = DmaStagedDecode(dev, shape.nh_kv)
+    kvb = workloads.kv_bytes(shape, lens)
+    res = {"layout": "request pool: one contiguous pinned row per request", "kv_bytes_per_step": kvb}
+    for name, fn in (("streamed_by_sms", lambda: kernel.decode(layer, q, sl, shape.scale, row_map=rm, x=x, out=out)),
+                     ("staged_by_copy_engines", lambda: stager.decode(layer, k, v, list(range(B)), lens, q, sl, shape.scale, rm, x=x, out=out))):
+        med, _ = _median_ms(fn, steps, warmup, torch.cuda.synchronize)
+        res[name] = {"ms_per_step": med, "gbs": kvb / med / 1e6}
+    get_context(dev.index).raise_on_status()
+    kernel.unregister_layer(layer)
+    return res
+
+
 def run_extend_probe(args, dev):
     r = measure_extend(dev, max(3, min(args.steps, 20)), args.warmup)
     print(json.dumps({"metric": "extend_attention_tflops", "value": r["attention_tflops"], "unit": "TFLOP/s",
@@ -578,6 +612,7 @@ def main():
     cpu_gbs, cpu_ms, cores, sample = cpu_reference_time(2, 1, lens, [0, 8]) if world == 1 else (None, None, None, None)
     # Secondary number, outside the timed region of the headline: the chunked-prefill path on this GPU.
     extend = measure_extend(dev, 10, 3) if world == 1 else None
+    request_pool = measure_request_pool(dev, lens) if world == 1 else None
 
     line = {
         "metric": METRIC, "value": kv_all_ranks / ms_hbm / 1e6, "unit": UNIT, "n_gpus": world,
@@ -606,6 +641,8 @@ def main():
     }
     if extend is not None:
         line["extend"] = extend
+    if request_pool is not None:
+        line["e2e_request_pool"] = request_pool
     if cpu_gbs is not None:
         line["cpu_baseline"] = {"value": cpu_gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
                                 "ms_per_step": cpu_ms}

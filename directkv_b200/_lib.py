@@ -74,6 +74,10 @@ class DecodeArgs(C.Structure):
         ("lse_out", C.c_void_p),
         ("partial_out", C.c_void_p),
         ("pos_offset", C.c_void_p),
+        ("kv_source_layer", C.c_int),
+        ("src_page_table", C.c_void_p),
+        ("src_pt_stride", C.c_int),
+        ("src_row_map", C.c_void_p),
     ]
 
 

@@ -940,7 +940,12 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
         DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
         DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
         const int g_total = a->nh_q / nh_kv;
-        const bool beside = a->batch > 0 && !use_mma(ctx, g_total, L.pool_on_host) && choose_g(ctx, g_total, L.pool_on_host) == 1 &&
+        bool rows_on_host = L.pool_on_host;              // where the streaming kernel will read from
+        if (a->kv_source_layer != 0) {
+            auto its = ctx->layers.find(a->kv_source_layer);
+            if (its != ctx->layers.end()) rows_on_host = its->second.pool_on_host;
+        }
+        const bool beside = a->batch > 0 && !use_mma(ctx, g_total, rows_on_host) && choose_g(ctx, g_total, rows_on_host) == 1 &&
                             effective_variant(ctx, 1) == 2;
         rc = launch_projection(ctx, L, a->x, a->batch, tok_pos, tok_slot, a->save_kv_cache != 0, kv_new,
                                reinterpret_cast<float*>(base + sp.splitk), ctx->side, beside);
@@ -958,8 +963,25 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
     AttnParams ap{};
     ap.q = static_cast<const __nv_bfloat16*>(a->q);
     ap.q_stride = a->q_stride;
+    // The past rows are read from the layer's own pool, or from a copy of them registered as another layer.
+    const LayerState* Lsrc = &L;
+    bool src_paged = paged;
     ap.page_table = a->page_table;
     ap.row_map = a->row_map;
+    ap.pt_stride = a->pt_stride;
+    if (a->kv_source_layer != 0) {
+        auto its = ctx->layers.find(a->kv_source_layer);
+        if (its == ctx->layers.end())
+            return fail(DKV_ERR_NOT_REGISTERED, "dkv_decode: kv_source_layer %d not registered", a->kv_source_layer);
+        Lsrc = &its->second;
+        DKV_REQUIRE(Lsrc->d.nh_kv == nh_kv, "kv_source_layer has %d KV heads, the layer %d", Lsrc->d.nh_kv, nh_kv);
+        src_paged = a->src_page_table != nullptr;
+        if (src_paged) DKV_REQUIRE(a->src_pt_stride > 0, "src_pt_stride must be positive");
+        else DKV_REQUIRE(Lsrc->d.row_stride > 0, "kv_source_layer was registered without row_stride; pass src_page_table");
+        ap.page_table = a->src_page_table;
+        ap.row_map = a->src_row_map;
+        ap.pt_stride = a->src_pt_stride;
+    }
     ap.seq_lens = a->seq_lens;
     ap.cum_tiles = cum;
     ap.partials = reinterpret_cast<float*>(base + sp.partials);
@@ -968,11 +990,10 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
     ap.nh_q = a->nh_q;
     ap.nh_kv = nh_kv;
     ap.g_total = a->nh_q / nh_kv;
-    ap.pt_stride = a->pt_stride;
-    ap.page_size = L.d.page_size;
-    ap.page_shift = L.page_shift;
-    ap.rows_per_box = L.rows_per_box;
-    ap.row_stride = L.d.row_stride;
+    ap.page_size = Lsrc->d.page_size;
+    ap.page_shift = Lsrc->page_shift;
+    ap.rows_per_box = Lsrc->rows_per_box;
+    ap.row_stride = Lsrc->d.row_stride;
     ap.n_new = n_new;
     ap.scale_log2 = a->softmax_scale * 1.4426950408889634f;
     MergeParams mp{};
@@ -990,7 +1011,7 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
             mp.x_count[r] = ex->count[r];
         }
     }
-    return launch_attention(ctx, L, ap, paged, mp, st, a->new_mode == DKV_NEW_PROJECT ? ctx->ev_join : nullptr);
+    return launch_attention(ctx, *Lsrc, ap, src_paged, mp, st, a->new_mode == DKV_NEW_PROJECT ? ctx->ev_join : nullptr);
 }
 
 #ifdef DKV_PP_TIMING

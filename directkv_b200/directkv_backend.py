@@ -22,6 +22,8 @@ What is different underneath
 
 from __future__ import annotations
 
+import os
+
 import logging
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Tuple
@@ -92,6 +94,10 @@ class DirectKVBackend(AttentionBackend):
         self._pool_cls = DirectKVRequestPool
         self._pool: Optional[DirectKVRequestPool] = None
         self._registered: set = set()
+        # Eager decode steps bring the past rows to HBM with the copy engines (DIRECTKV_B200_DMA_STAGING=0: stream
+        # them with the SMs as under CUDA graphs).
+        self._dma_staging = os.environ.get("DIRECTKV_B200_DMA_STAGING", "1") != "0"
+        self._stager = None
         self._token_registered: Dict[int, int] = {}
         self._active_req_ids: set = set()
         self._last_seen: Dict[int, int] = {}
@@ -305,10 +311,20 @@ class DirectKVBackend(AttentionBackend):
         q2 = q.reshape(bs, self.num_q_heads * self.head_dim).contiguous()
         if x is None or lid not in self._registered:
             return self._decode_token_pool(q2, k, v, layer, forward_batch)
-        return kernel.decode(
-            lid, q2, meta.seq_lens_dev[:bs], float(layer.scaling), row_map=meta.rows_dev[:bs],
-            x=x.reshape(bs, self.hidden_size).contiguous(), save_kv_cache=save_kv_cache,
-        )
+        x2 = x.reshape(bs, self.hidden_size).contiguous()
+        if self._dma_staging and save_kv_cache and not torch.cuda.is_current_stream_capturing():
+            # Eager step over the host-pinned request pool: the copy engines bring the past rows to HBM at the
+            # full rate of the host link and the kernels attend that copy (directkv_b200/staging.py).
+            if self._stager is None:
+                from .staging import DmaStagedDecode
+
+                self._stager = DmaStagedDecode(self.device, self.num_kv_heads, self._pool.dtype)
+            li = lid - self._pool.start_layer
+            rows = [self._pool.row_of(r) for r in meta.req_pool_indices_cpu[:bs]]
+            return self._stager.decode(lid, self._pool.k_pool[li], self._pool.v_pool[li], rows, meta.seq_lens_cpu[:bs],
+                                       q2, meta.seq_lens_dev[:bs], float(layer.scaling), meta.rows_dev[:bs], x=x2)
+        return kernel.decode(lid, q2, meta.seq_lens_dev[:bs], float(layer.scaling), row_map=meta.rows_dev[:bs], x=x2,
+                             save_kv_cache=save_kv_cache)
 
     def _token_layer(self, layer, forward_batch) -> int:
         """Engine registration of SGLang's token-indexed pool for this layer (page size 1 = per-token slots)."""

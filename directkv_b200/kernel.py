@@ -124,6 +124,9 @@ def decode(
     normalized: bool = True,
     pos_offset: Optional[torch.Tensor] = None,   # [B] int32 CUDA: added to seq_len-1 for the RoPE position
     exchange=None,                               # handle of a connected peer-memory exchange (sharding.PartialExchange)
+    kv_source_layer: int = 0,                    # attend a copy of the past rows registered as this layer (0: off)
+    src_page_table: Optional[torch.Tensor] = None,   # addressing of the copy (its page size) ...
+    src_row_map: Optional[torch.Tensor] = None,      # ... or its rows
 ) -> Optional[torch.Tensor]:
     """One decode step of one registered layer for a ragged batch.  Returns O with q's shape.
 
@@ -160,6 +163,13 @@ def decode(
              and partial_out.numel() == b * nh_q * PARTIAL_STRIDE, "partial_out must be [B, NH_q, 132] fp32 CUDA")
     if pos_offset is not None:
         _chk(pos_offset.is_cuda and pos_offset.dtype == torch.int32 and pos_offset.numel() == b, "pos_offset must be [B] int32 CUDA")
+    if src_page_table is not None:
+        _chk(kv_source_layer != 0 and src_page_table.is_cuda and src_page_table.dtype == torch.int32
+             and src_page_table.dim() == 2 and src_page_table.stride(1) == 1,
+             "src_page_table needs kv_source_layer and must be 2D int32 CUDA with unit inner stride")
+    if src_row_map is not None:
+        _chk(kv_source_layer != 0 and src_row_map.is_cuda and src_row_map.dtype == torch.int32 and src_row_map.numel() == b,
+             "src_row_map needs kv_source_layer and must be [B] int32 CUDA")
     if b == 0:
         return out
     a = DecodeArgs(
@@ -169,6 +179,8 @@ def decode(
         row_map=_ptr(row_map), new_mode=mode, x=_ptr(x), k_new=_ptr(k_new), v_new=_ptr(v_new),
         save_kv_cache=1 if save_kv_cache else 0, softmax_scale=float(softmax_scale),
         lse_out=_ptr(lse_out), partial_out=_ptr(partial_out), pos_offset=_ptr(pos_offset),
+        kv_source_layer=int(kv_source_layer), src_page_table=_ptr(src_page_table),
+        src_pt_stride=0 if src_page_table is None else src_page_table.stride(0), src_row_map=_ptr(src_row_map),
     )
     ctx = get_context(q.device.index)
     if exchange is not None:

@@ -144,6 +144,15 @@ typedef struct {
     float*         partial_out;  /* [batch, nh_q, 132] unnormalised (O[128], m_log2, l, pad) or NULL */
     const int32_t* pos_offset;   /* [batch] or NULL: added to seq_lens[b] - 1 to get the new token's absolute
                                     (RoPE) position when this pool holds only a later part of the sequence */
+    /* Attend a COPY of the past rows instead of the layer's own pool (0 / NULL: off).  kv_source_layer is another
+     * registered layer - typically rows that the copy engines brought from the host pool into HBM, which reach
+     * the full rate of the host link where reads issued by the SMs reach 0.92 of it - addressed by
+     * src_page_table / src_pt_stride (its page size) or src_row_map (its row_stride).  The new token is still
+     * projected with, positioned by and stored to `layer_id` through page_table / row_map above. */
+    int            kv_source_layer;
+    const int32_t* src_page_table;
+    int            src_pt_stride;
+    const int32_t* src_row_map;
 } dkv_decode_args;
 
 int dkv_decode(dkv_context* ctx, const dkv_decode_args* args, void* stream);

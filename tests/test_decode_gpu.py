@@ -263,6 +263,52 @@ def test_config2_full_size_properties():
     kernel.unregister_layer(62)
 
 
+def test_dma_staged_decode_matches_streaming():
+    """Request-pool layout in pinned host memory: the past rows copied to HBM by cudaMemcpyAsync and attended there
+    give the same bits as streaming them from the host pool (same 16-token tiles in the same order), and the new
+    token lands in the host pool either way."""
+    from directkv_b200.staging import DmaStagedDecode
+
+    shape = _shape(256, 8, 2)
+    rows_total, s_pad = 5, 512
+    g = torch.Generator().manual_seed(123)
+    K = (torch.randn(rows_total, s_pad, 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+    V = (torch.randn(rows_total, s_pad, 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+    wk = (torch.randn(2, 128, 256, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    wv = (torch.randn(2, 128, 256, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    cs = orc.build_cos_sin(s_pad, 128, 10000.0).to(DEV)
+    lens, rows = [200, 1, 65, 333], [4, 0, 2, 1]
+    q = torch.randn(4, 8 * 128, generator=g).to(torch.bfloat16).to(DEV)
+    x = torch.randn(4, 256, generator=g).to(torch.bfloat16).to(DEV)
+    sl = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    rm = torch.tensor(rows, dtype=torch.int32, device=DEV)
+    outs, pools = [], []
+    # The copy lives in HBM, where four query heads per KV head would pick the tensor-core form of the streaming
+    # kernel; with it switched off both runs execute the same arithmetic in the same order.
+    get_context(0).set("attn_mma", 0)
+    for staged in (False, True, True):
+        if len(outs) == 2:
+            get_context(0).set("attn_mma", -1)
+        Kp, Vp = K.clone().pin_memory(), V.clone().pin_memory()
+        kernel.register_layer(81, Kp, Vp, wk, wv, cs, row_stride=s_pad)
+        if staged:
+            st = DmaStagedDecode(torch.device(DEV), 2)
+            o = st.decode(81, Kp, Vp, rows, lens, q, sl, shape.scale, rm, x=x)
+        else:
+            o = kernel.decode(81, q, sl, shape.scale, row_map=rm, x=x)
+        torch.cuda.synchronize()
+        get_context(0).raise_on_status()
+        outs.append(o.clone())
+        pools.append((Kp.clone(), Vp.clone()))
+        kernel.unregister_layer(81)
+    assert torch.equal(outs[0], outs[1])
+    assert (outs[2].float() - outs[0].float()).abs().max().item() < 1e-2           # tensor-core form on the copy
+    assert torch.equal(pools[0][0], pools[1][0]) and torch.equal(pools[0][1], pools[1][1])
+    assert torch.equal(pools[0][0], pools[2][0])
+    for b, (r, n) in enumerate(zip(rows, lens)):
+        assert not torch.equal(pools[1][0][r, n - 1], K[r, n - 1])      # the new token was written to the host pool
+
+
 def test_errors():
     with pytest.raises(RuntimeError, match="not registered"):
         kernel.decode(999, torch.zeros(1, 128, dtype=torch.bfloat16, device=DEV),
