@@ -309,6 +309,33 @@ def test_dma_staged_decode_matches_streaming():
         assert not torch.equal(pools[1][0][r, n - 1], K[r, n - 1])      # the new token was written to the host pool
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_randomised_configurations(seed):
+    """Seeded random draws over head groupings, page sizes, batch sizes, lengths, where the pool lives, how the new
+    token arrives and which forms of the kernels run; every draw is compared with the oracle."""
+    import random
+
+    rnd = random.Random(9000 + seed)
+    nh_kv = rnd.choice([1, 2, 3, 4, 8])
+    g = rnd.choice([1, 1, 2, 3, 4, 6, 8, 16])
+    hidden = rnd.choice([64, 192, 512, 1024])
+    page = rnd.choice([1, 2, 4, 8, 16, 32, 64])
+    batch = rnd.choice([1, 2, 3, 7, 16, 40])
+    hi = rnd.choice([20, 100, 700, 3000])
+    lens = [rnd.randint(1, hi) for _ in range(batch)]
+    mode = rnd.choice(["project", "project", "given", "none"])
+    if mode == "none":
+        lens = [max(2, n) for n in lens]
+    ctx = get_context(0)
+    ctx.set("proj_decode", rnd.choice([-1, 0, 1]))
+    try:
+        _run_decode(_shape(hidden, nh_kv * g, nh_kv, rope=(mode == "project" and rnd.random() < 0.7)), lens, page,
+                    cfg_id=300 + seed, kv_on_host=rnd.random() < 0.5, mode=mode, variant=rnd.choice([-1, 0, 1, 2]),
+                    mma=rnd.choice([-1, -1, 0, 1]) if g <= 16 else -1)
+    finally:
+        ctx.set("proj_decode", -1)
+
+
 def test_errors():
     with pytest.raises(RuntimeError, match="not registered"):
         kernel.decode(999, torch.zeros(1, 128, dtype=torch.bfloat16, device=DEV),
