@@ -299,3 +299,226 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 }
 
 }  // namespace dkv
+
+namespace dkv {
+
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// Variant for up to 8 query heads per KV head: the roles of the product are swapped, tokens (then head
+// dimensions) on the 16-row M side and the query heads on the 8-column N side,
+//
+//   S^T[16 tokens x 8 q] = K_tile[16 x 128] . Q^T[128 x 8]        8 mma.m16n8k16 (A = K by ldmatrix, B = Q in registers)
+//   O^T[128 d x 8 q]    += V_tile^T[128 x 16] . P^T[16 x 8]       8 mma.m16n8k16 (A = V by ldmatrix.trans, B = P^T)
+//
+// which halves the tensor-core instructions and the accumulator registers of the 16-row form above (O^T: 32
+// registers, Q: 16), so that a 16-warp CTA stays near 100 registers per thread and leaves room on the SM for
+// the decode projection.  P^T reaches its B-fragment layout with one movmatrix per 8 tokens.  The reference maximum
+// of a query head is shared by the eight lanes that hold its columns; it moves only when some score exceeds it by
+// more than 2^8 (one warp vote per tile), so the three-shuffle reduction runs on the first tiles only.
+template <int NWARPS, int NST>
+__global__ void __maxnreg__(NWARPS == 16 ? 104 : NWARPS == 12 ? 168 : 232)   // 16 warps: room for the decode projection
+attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                         const AttnParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r4 = lane >> 2, c4 = lane & 3;
+    uint8_t* wbase = smem + static_cast<size_t>(warp) * NST * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(NWARPS) * NST * kStageBytes) + warp * NST;
+
+    const int G = p.g_total / p.nsub;                 // query heads per record, <= 8
+    const int nhs = p.nh_kv * p.nsub;
+    const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
+    const long long qn = (U + p.total_warps - 1) / p.total_warps;
+    const int gw = blockIdx.x * NWARPS + warp;
+    const long long u0 = static_cast<long long>(gw) * qn;
+    const long long u1 = (u0 + qn < U) ? u0 + qn : U;
+    if (u0 >= u1) return;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < NST; ++s) mbar_init(&bars[s], 1);
+        fence_mbar_init();
+        fence_proxy_async_smem();
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+    }
+    __syncwarp();
+
+    TileCursor cc, pc;
+    cc.locate(p, u0, nhs);
+    pc = cc;
+    long long pu = u0;
+#pragma unroll
+    for (int s = 0; s < NST; ++s) {
+        if (pu < u1) {
+            if (lane == 0) issue_tile_sw(p, &tmK, &tmV, pc, wbase + s * kStageBytes, &bars[s]);
+            pc.advance(p, nhs);
+            ++pu;
+        }
+    }
+
+    uint32_t phase_bits = 0;
+    int stage = 0;
+    bool failed = false;
+
+    uint32_t qb[8][2];            // B fragments of Q^T: query head r4, dims 16 ks + 2 c4 (+8)
+    float o[8][4];                // O^T: dims 16 mt + r4 (+8) x query heads 2 c4, 2 c4 + 1
+    float m0 = -INFINITY, m1 = -INFINITY;   // reference maxima of query heads 2 c4 and 2 c4 + 1 (same in all r4 lanes)
+    float l0 = 0.f, l1 = 0.f;               // this lane's share of the sums (its tokens r4 and r4 + 8)
+    int past_b = 0;
+    bool seg_open = false;
+
+    for (long long u = u0; u < u1; ++u) {
+        if (!seg_open) {
+            const int h = cc.hs / p.nsub, sub = cc.hs - h * p.nsub;
+            const __nv_bfloat16* qrow =
+                p.q + static_cast<long long>(cc.b) * p.q_stride + static_cast<long long>(h * p.g_total + sub * G + r4) * kHeadDim;
+            const bool have = r4 < G;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                qb[ks][0] = have ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c4) : 0u;
+                qb[ks][1] = have ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * c4 + 8) : 0u;
+            }
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) o[mt][0] = o[mt][1] = o[mt][2] = o[mt][3] = 0.f;
+            m0 = m1 = -INFINITY;
+            l0 = l1 = 0.f;
+            past_b = p.seq_lens[cc.b] - p.n_new;
+            seg_open = true;
+        }
+
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(&bars[stage], (phase_bits >> stage) & 1u))) {
+            failed = true;
+            break;
+        }
+        phase_bits ^= (1u << stage);
+        uint8_t* sK = wbase + stage * kStageBytes;
+        uint8_t* sV = sK + 2 * kMmaHalfBytes;
+        const uint32_t sK_a = smem_u32(sK), sV_a = smem_u32(sV);
+        const int valid = past_b - cc.tile * kTileTokens;
+
+        if (valid < kTileTokens) {
+            // Rows past the request's last token may hold anything; their probabilities are zero, but the
+            // tensor core still multiplies, so V must be finite there.
+            for (int idx = lane; idx < (kTileTokens - valid) * 16; idx += 32)
+                *reinterpret_cast<uint4*>(sV + sw_tile_off(valid + (idx >> 4), idx & 15)) = make_uint4(0, 0, 0, 0);
+            fence_proxy_async_smem();   // these stores precede the next TMA write into the same stage
+            __syncwarp();
+        }
+
+        // ---- S^T = K Q^T: this lane gets tokens r4, r4 + 8 of query heads 2 c4, 2 c4 + 1 ----
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            const int tok = (mi & 1) * 8 + r;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t a[4];
+                ldmatrix_x4(a, sK_a + sw_tile_off(tok, 2 * ks + (mi >> 1)));
+                mma_bf16_16816(s, a, qb[ks][0], qb[ks][1]);
+            }
+        }
+        const bool t_lo = r4 < valid, t_hi = r4 + 8 < valid;
+        const float v00 = t_lo ? s[0] * p.scale_log2 : -INFINITY, v01 = t_lo ? s[1] * p.scale_log2 : -INFINITY;
+        const float v10 = t_hi ? s[2] * p.scale_log2 : -INFINITY, v11 = t_hi ? s[3] * p.scale_log2 : -INFINITY;
+        float x0 = fmaxf(v00, v10), x1 = fmaxf(v01, v11);
+        const bool grow = (x0 > m0 + 8.f) || (x1 > m1 + 8.f) || (m0 == -INFINITY && x0 > -INFINITY) ||
+                          (m1 == -INFINITY && x1 > -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+            for (int sh = 4; sh < 32; sh <<= 1) {
+                x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, sh));
+                x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, sh));
+            }
+            const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+            const float a0 = (n0 == -INFINITY) ? 1.f : exp2f(m0 - n0), a1 = (n1 == -INFINITY) ? 1.f : exp2f(m1 - n1);
+            m0 = n0;
+            m1 = n1;
+            l0 *= a0;
+            l1 *= a1;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                o[mt][0] *= a0;
+                o[mt][1] *= a1;
+                o[mt][2] *= a0;
+                o[mt][3] *= a1;
+            }
+        }
+        const float u0m = (m0 == -INFINITY) ? 0.f : m0, u1m = (m1 == -INFINITY) ? 0.f : m1;
+        const float p00 = exp2f(v00 - u0m), p01 = exp2f(v01 - u1m), p10 = exp2f(v10 - u0m), p11 = exp2f(v11 - u1m);
+        l0 += p00 + p10;
+        l1 += p01 + p11;
+        // P^T (tokens x heads) in accumulator layout -> B fragments (token pairs of head r4) by transposing 8 x 8 blocks.
+        const uint32_t pb0 = movmatrix_trans(pack_bf16x2(p00, p01));
+        const uint32_t pb1 = movmatrix_trans(pack_bf16x2(p10, p11));
+        // ---- O^T += V^T P^T ----
+        {
+            const int mi = lane >> 3, r = lane & 7;
+            const int tok = (mi >> 1) * 8 + r;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, sV_a + sw_tile_off(tok, 2 * mt + (mi & 1)));
+                mma_bf16_16816(o[mt], a, pb0, pb1);
+            }
+        }
+        __syncwarp();
+
+        if (pu < u1) {
+            if (lane == 0) issue_tile_sw(p, &tmK, &tmV, pc, wbase + stage * kStageBytes, &bars[stage]);
+            pc.advance(p, nhs);
+            ++pu;
+        }
+        stage = (stage + 1 == NST) ? 0 : stage + 1;
+
+        const bool last_of_seg = (cc.tile + 1 == cc.tiles_b) || (u + 1 == u1);
+        if (last_of_seg) {
+            const int seg = cc.b * nhs + cc.hs;
+            float* out = p.partials + static_cast<size_t>(gw + seg) * (G * kPartialStride);
+            float lt0 = l0, lt1 = l1;
+#pragma unroll
+            for (int sh = 4; sh < 32; sh <<= 1) {
+                lt0 += __shfl_xor_sync(0xffffffffu, lt0, sh);
+                lt1 += __shfl_xor_sync(0xffffffffu, lt1, sh);
+            }
+            const int q0 = 2 * c4, q1 = 2 * c4 + 1;
+            if (q0 < G) {
+                float* og = out + q0 * kPartialStride;
+#pragma unroll
+                for (int mt = 0; mt < 8; ++mt) {
+                    og[16 * mt + r4] = o[mt][0];
+                    og[16 * mt + r4 + 8] = o[mt][2];
+                }
+                if (r4 == 0) {
+                    og[128] = m0;
+                    og[129] = lt0;
+                }
+            }
+            if (q1 < G) {
+                float* og = out + q1 * kPartialStride;
+#pragma unroll
+                for (int mt = 0; mt < 8; ++mt) {
+                    og[16 * mt + r4] = o[mt][1];
+                    og[16 * mt + r4 + 8] = o[mt][3];
+                }
+                if (r4 == 0) {
+                    og[128] = m1;
+                    og[129] = lt1;
+                }
+            }
+            seg_open = false;
+        }
+        cc.advance(p, nhs);
+    }
+
+    if (failed) {
+        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+        for (int s = 0; s < NST; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
+    }
+}
+
+}  // namespace dkv

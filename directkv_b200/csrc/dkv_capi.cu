@@ -146,6 +146,7 @@ struct dkv_context {
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
     int proj_wide = 1;                  // 256-token projection tiles when there are more 128-token tiles than SMs
     int proj_decode = -1;               // swapped-operand projection kernel: -1 when it can run under the streaming kernel; 0 never; 1 whenever T <= 512
+    int attn_mma8 = 1;                  // tensor-core form with the query heads on the N side when <= 8 share a KV head (0: 16-row form)
     int attn_mma = -1;                  // -1: tensor-core inner product when 3..16 query heads share a KV head; 0 never; 1 always
     int extend_pingpong = 1;            // two query tiles per CTA with specialised warps (0: one tile, four warps)
     int extend_rowwise = 0;             // 1: extend attends row by row with the decode kernels (reference path for tests)
@@ -397,6 +398,35 @@ cudaError_t attn_mma_dispatch(int variant, int ctas, const CUtensorMap& tmK, con
         case 1: return attn_mma_launch<12, 2>(ctas, tmK, tmV, p, st);
         default: return attn_mma_launch<16, 1>(ctas, tmK, tmV, p, st);
     }
+}
+
+template <int NW, int NST>
+cudaError_t attn_mma8_launch(int ctas, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p, cudaStream_t st) {
+    attn_partial_mma8_kernel<NW, NST><<<ctas, NW * 32, attn_smem_bytes<1, NW, NST>(), st>>>(tmK, tmV, p);
+    return cudaGetLastError();
+}
+
+cudaError_t attn_mma8_dispatch(int variant, int ctas, const CUtensorMap& tmK, const CUtensorMap& tmV, const AttnParams& p,
+                               cudaStream_t st) {
+    switch (variant) {
+        case 0: return attn_mma8_launch<8, 3>(ctas, tmK, tmV, p, st);
+        case 1: return attn_mma8_launch<12, 2>(ctas, tmK, tmV, p, st);
+        default: return attn_mma8_launch<16, 1>(ctas, tmK, tmV, p, st);
+    }
+}
+
+// Kernels that are meant to share an SM ask for the largest shared-memory carve-out, so that whichever of them
+// arrives first does not leave the SM configured too small for the other.
+template <typename K>
+cudaError_t prefer_max_shared(K kernel) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
+template <int NW, int NST>
+cudaError_t attn_mma8_set_attr() {
+    cudaError_t e = cudaFuncSetAttribute(attn_partial_mma8_kernel<NW, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(attn_smem_bytes<1, NW, NST>()));
+    return e != cudaSuccess ? e : prefer_max_shared(attn_partial_mma8_kernel<NW, NST>);
 }
 
 template <int NW, int NST>
@@ -677,7 +707,8 @@ int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool
         if (ctx->attn_events_used < ctx->attn_events.size()) ev = &ctx->attn_events[ctx->attn_events_used++];
     }
     if (ev) DKV_CUDA(cudaEventRecord(ev->first, st));
-    if (mma) e = attn_mma_dispatch(mma_variant, ctas, tmK, tmV, ap, st);
+    if (mma && G <= 8 && ctx->attn_mma8 != 0) e = attn_mma8_dispatch(mma_variant, ctas, tmK, tmV, ap, st);
+    else if (mma) e = attn_mma_dispatch(mma_variant, ctas, tmK, tmV, ap, st);
     else if (G == 4) e = attn_dispatch<4>(effective_variant(ctx, 4), ctas, tmK, tmV, ap, st);
     else if (G == 2) e = attn_dispatch<2>(effective_variant(ctx, 2), ctas, tmK, tmV, ap, st);
     else e = attn_dispatch<1>(effective_variant(ctx, 1), ctas, tmK, tmV, ap, st);
@@ -741,6 +772,9 @@ int dkv_context_create(int device, dkv_context** out) {
     if (e == cudaSuccess) e = attn_mma_set_attr<8, 3>();
     if (e == cudaSuccess) e = attn_mma_set_attr<12, 2>();
     if (e == cudaSuccess) e = attn_mma_set_attr<16, 1>();
+    if (e == cudaSuccess) e = attn_mma8_set_attr<8, 3>();
+    if (e == cudaSuccess) e = attn_mma8_set_attr<12, 2>();
+    if (e == cudaSuccess) e = attn_mma8_set_attr<16, 1>();
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(extend_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kExtSmem + 1024);
     if (e == cudaSuccess)
@@ -754,6 +788,8 @@ int dkv_context_create(int device, dkv_context** out) {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(proj_rope_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(pd_smem_bytes(kPdMaxTokens)));
+    if (e == cudaSuccess) e = prefer_max_shared(proj_rope_decode_kernel);
+    if (e == cudaSuccess) e = prefer_max_shared(attn_partial_kernel<1, 16, 1>);
     if (e != cudaSuccess) {
         delete ctx;
         return fail(DKV_ERR_CUDA, "context set-up failed: %s", cudaGetErrorString(e));
@@ -804,6 +840,8 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "proj_decode")) {
         DKV_REQUIRE(value >= -1 && value <= 1, "proj_decode must be -1, 0 or 1");
         ctx->proj_decode = value;
+    } else if (!strcmp(key, "attn_mma8")) {
+        ctx->attn_mma8 = value != 0;
     } else if (!strcmp(key, "attn_mma")) {
         DKV_REQUIRE(value >= -1 && value <= 1, "attn_mma must be -1, 0 or 1");
         ctx->attn_mma = value;
@@ -945,8 +983,13 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
             auto its = ctx->layers.find(a->kv_source_layer);
             if (its != ctx->layers.end()) rows_on_host = its->second.pool_on_host;
         }
-        const bool beside = a->batch > 0 && !use_mma(ctx, g_total, rows_on_host) && choose_g(ctx, g_total, rows_on_host) == 1 &&
-                            effective_variant(ctx, 1) == 2;
+        // Forms of the streaming kernel that leave the projection registers and shared memory on every SM: the
+        // 16-warp CUDA-core form (one query head per KV head) and the 16-warp tensor-core form for up to 8.
+        const bool mma_form = use_mma(ctx, g_total, rows_on_host);
+        const int G_form = choose_g(ctx, g_total, rows_on_host);
+        const bool beside = a->batch > 0 &&
+                            ((!mma_form && G_form == 1 && effective_variant(ctx, 1) == 2) ||
+                             (mma_form && G_form <= 8 && ctx->attn_mma8 != 0 && (ctx->attn_variant < 0 || ctx->attn_variant == 2)));
         rc = launch_projection(ctx, L, a->x, a->batch, tok_pos, tok_slot, a->save_kv_cache != 0, kv_new,
                                reinterpret_cast<float*>(base + sp.splitk), ctx->side, beside);
         if (rc != DKV_OK) return rc;
