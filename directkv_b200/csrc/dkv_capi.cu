@@ -147,7 +147,7 @@ struct dkv_context {
     int proj_wide = 1;                  // 256-token projection tiles when there are more 128-token tiles than SMs
     int proj_decode = -1;               // swapped-operand projection kernel: -1 when it can run under the streaming kernel; 0 never; 1 whenever T <= 512
     int attn_mma8 = 1;                  // tensor-core form with the query heads on the N side when <= 8 share a KV head (0: 16-row form)
-    int attn_mma = -1;                  // -1: tensor-core inner product when 3..16 query heads share a KV head; 0 never; 1 always
+    int attn_mma = -1;                  // -1: tensor-core inner product when 2..16 query heads share a KV head of an HBM pool; 0 never; 1 always
     int extend_pingpong = 1;            // two query tiles per CTA with specialised warps (0: one tile, four warps)
     int extend_rowwise = 0;             // 1: extend attends row by row with the decode kernels (reference path for tests)
     // Profiling: kernel launches issued, and CUDA-event pairs around the streaming kernel.
@@ -452,7 +452,7 @@ struct ScratchPlan {
 // half-size read requests and cost 20 % of the link (40 against 51 GB/s), and the link, not the instruction
 // issue rate, bounds a host-resident pool: automatic choice only for pools in HBM.
 bool use_mma(const dkv_context* ctx, int g_total, bool pool_on_host) {
-    return ctx->attn_mma == 1 || (ctx->attn_mma < 0 && g_total >= 3 && !pool_on_host);
+    return ctx->attn_mma == 1 || (ctx->attn_mma < 0 && g_total >= 2 && !pool_on_host);
 }
 
 // Query heads that share one pass over a KV head: the mma kernel takes up to 16 rows (the largest divisor of

@@ -65,7 +65,7 @@ int dkv_context_destroy(dkv_context* ctx);
 int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv, int hidden);
 
 /* Knobs, by name: "attn_variant" (-1 = automatic, 0..2), "attn_mma" (-1 = automatic: warp-level tensor-core
- * inner product when 3..16 query heads share a KV head; 0 = never; 1 = always), "attn_mma8" (1 = query heads on the N
+ * inner product when 2..16 query heads share a KV head of a pool in HBM; 0 = never; 1 = always), "attn_mma8" (1 = query heads on the N
  * side of the tensor-core product when at most 8 share a KV head, default; 0 = always the 16-row form), "extend_rowwise" (0/1),
  * "extend_pingpong" (1 = two query tiles per CTA, default; 0 = first form of the extend kernel), "proj_decode"
  * (-1 = use the decode-batch projection kernel where it can run under the streaming kernel, 0 = never, 1 = for
