@@ -186,7 +186,7 @@ namespace {
 __global__ void extend_prep_kernel(int B, int S_new, int seqlen_past_host, const int* __restrict__ n_past_blocks_dev,
                                    int is_causal, const int* __restrict__ row_map, long long row_stride,
                                    int* __restrict__ vseq, int* __restrict__ vrow, int* __restrict__ tok_pos,
-                                   int* __restrict__ tok_slot) {
+                                   int* __restrict__ tok_slot, int stage_stride, int* __restrict__ tok_stage_slot) {
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= B * S_new) return;
     const int b = v / S_new, i = v - b * S_new;
@@ -196,6 +196,7 @@ __global__ void extend_prep_kernel(int B, int S_new, int seqlen_past_host, const
     vrow[v] = row;
     tok_pos[v] = past + i;
     tok_slot[v] = static_cast<int>(static_cast<long long>(row) * row_stride + past + i);
+    if (tok_stage_slot != nullptr) tok_stage_slot[v] = b * stage_stride + past + i;   // row of the staging copy [B, stage_stride]
 }
 
 // Largest b with prefix[b] <= v (prefix ascending, prefix[0] == 0).
@@ -210,15 +211,45 @@ __device__ __forceinline__ int find_request(const int* __restrict__ prefix, int 
 }
 
 // Ragged extend: position and pool slot of every new row of the packed batch.
+// kv_off != nullptr: the new rows are projected into the staging copy (request b starts at row kv_off[b]) and
+// tok_pool_slot receives the slot of the layer's own pool, for the write-back that follows.
 __global__ void extend_prep_ragged_kernel(int B, int T, const int* __restrict__ q_row0, const int* __restrict__ past,
-                                          const int* __restrict__ rows, long long row_stride, int* __restrict__ tok_pos,
-                                          int* __restrict__ tok_slot) {
+                                          const int* __restrict__ rows, long long row_stride, const int* __restrict__ kv_off,
+                                          int* __restrict__ tok_pos, int* __restrict__ tok_slot,
+                                          int* __restrict__ tok_pool_slot) {
     const int v = blockIdx.x * blockDim.x + threadIdx.x;
     if (v >= T) return;
     const int b = find_request(q_row0, B, v);
     const int i = v - q_row0[b];
     tok_pos[v] = past[b] + i;
-    tok_slot[v] = static_cast<int>(static_cast<long long>(rows[b]) * row_stride + past[b] + i);
+    const int pool_slot = static_cast<int>(static_cast<long long>(rows[b]) * row_stride + past[b] + i);
+    if (kv_off != nullptr) {
+        tok_slot[v] = kv_off[b] + past[b] + i;
+        tok_pool_slot[v] = pool_slot;
+    } else {
+        tok_slot[v] = pool_slot;
+    }
+}
+
+// Write-back of freshly projected rows from the staging copy to the layer's (host) pool: one warp per row and
+// tensor half, 16-byte stores; runs on the side stream while the attention reads the staging copy.
+__global__ void __launch_bounds__(256) unstage_rows_kernel(uint4* __restrict__ k_pool, uint4* __restrict__ v_pool,
+                                                           const uint4* __restrict__ k_stage, const uint4* __restrict__ v_stage,
+                                                           const int* __restrict__ stage_slot, const int* __restrict__ pool_slot,
+                                                           long long n_rows, int row_vec, long long n_slots,
+                                                           unsigned int* status) {
+    const long long total = n_rows * row_vec;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const long long r = i / row_vec, c = i - r * row_vec;
+        const long long dst = pool_slot[r];
+        if (dst < 0 || dst >= n_slots) {
+            if (c == 0) atomicOr(status, dkv::kStatusBadSlot);
+            continue;
+        }
+        k_pool[dst * row_vec + c] = k_stage[static_cast<long long>(stage_slot[r]) * row_vec + c];
+        v_pool[dst * row_vec + c] = v_stage[static_cast<long long>(stage_slot[r]) * row_vec + c];
+    }
 }
 
 // Ragged extend over a host or paged pool: rows [0, past_b + s_new_b) of every request, one after the other, into
@@ -229,13 +260,15 @@ __global__ void __launch_bounds__(256) stage_rows_ragged_kernel(uint4* __restric
                                                                 const int* __restrict__ kv_off,
                                                                 const int* __restrict__ rows, long long row_stride,
                                                                 int row_vec, const int* __restrict__ page_table,
-                                                                long long pt_stride, int page_shift) {
+                                                                long long pt_stride, int page_shift,
+                                                                const int* __restrict__ past_only) {
     const long long total = static_cast<long long>(kv_off[B]) * row_vec;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
         const long long srow = i / row_vec;
         const int b = find_request(kv_off, B, srow);
         const long long pos = srow - kv_off[b];
+        if (past_only != nullptr && pos >= past_only[b]) continue;   // the new rows are projected straight into the copy
         const long long row = rows[b];
         long long slot;
         if (page_table != nullptr)
@@ -318,7 +351,7 @@ __global__ void __launch_bounds__(256) stage_rows_kernel(uint4* __restrict__ k_d
                                                          const int* __restrict__ row_map, long long row_stride, int B,
                                                          int s_total, int row_vec /* nh * 16 */,
                                                          const int* __restrict__ page_table, long long pt_stride,
-                                                         int page_shift) {
+                                                         int page_shift, int past_only /* < 0: every row */) {
     const long long per_req = static_cast<long long>(s_total) * row_vec;
     const long long total = per_req * B;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
@@ -326,6 +359,7 @@ __global__ void __launch_bounds__(256) stage_rows_kernel(uint4* __restrict__ k_d
         const int b = static_cast<int>(i / per_req);
         const long long r = i - b * per_req;
         const long long row = row_map ? row_map[b] : b;
+        if (past_only >= 0 && r / row_vec >= past_only) continue;    // the new rows are projected straight into the copy
         long long src;
         if (page_table != nullptr) {
             // Paged pool: position -> slot through the request's row of the page table; the staged copy is contiguous.
@@ -641,7 +675,7 @@ unsigned long long* pp_timing_buffer() {
 // Projection of T rows of X with RoPE and write-back (tcgen05 kernel).
 int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int T, const int* tok_pos,
                       const int* tok_slot, bool store_pool, __nv_bfloat16* kv_new, float* splitk, cudaStream_t st,
-                      bool beside_streaming = false) {
+                      bool beside_streaming = false, void* k_dst = nullptr, void* v_dst = nullptr, long long n_slots_dst = 0) {
     // The swapped-operand kernel pays off where it runs UNDER the streaming kernel (the 16-warp CUDA-core form
     // leaves it registers and shared memory); alone, the 128-token-tile kernel with its deeper ring is faster.
     const bool small = T <= kPdMaxBatch && (ctx->proj_decode == 1 || (ctx->proj_decode < 0 && beside_streaming));
@@ -663,9 +697,10 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
     pp.tok_slot = tok_slot;
     pp.cos_sin = L.d.cos_sin;
     pp.max_pos = L.d.max_pos;
-    pp.k_pool = store_pool ? static_cast<__nv_bfloat16*>(L.k_dev) : nullptr;
-    pp.v_pool = store_pool ? static_cast<__nv_bfloat16*>(L.v_dev) : nullptr;
-    pp.n_slots = L.d.n_slots;
+    // The rows go to the layer's pool, or (k_dst given) to a staging copy of it whose slots tok_slot addresses.
+    pp.k_pool = store_pool ? static_cast<__nv_bfloat16*>(k_dst ? k_dst : L.k_dev) : nullptr;
+    pp.v_pool = store_pool ? static_cast<__nv_bfloat16*>(k_dst ? v_dst : L.v_dev) : nullptr;
+    pp.n_slots = k_dst ? n_slots_dst : L.d.n_slots;
     pp.kv_new = kv_new;
     pp.splitk_scratch = splitk;
     pp.tile_counters = ctx->counters;
@@ -1206,6 +1241,9 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
     const bool tensor_path = !ctx->extend_rowwise || paged;
     const bool stage = paged || (!ctx->extend_rowwise && L.pool_on_host && n_past_blocks_dev == nullptr &&
                                  static_cast<long long>(S_new) * (nh_q / nh_kv) > kExtTile);
+    // With a staging copy the new rows are projected straight into it (the attention reads them there) and reach
+    // the host pool from the copy on the side stream, while the attention runs.
+    const bool proj_to_stage = project && stage;
     const size_t stage_bytes = stage ? static_cast<size_t>(B) * s_total_host * nh_kv * 256 : 0;
     ScratchPlan sp = plan_scratch(ctx, rows, nh_q, nh_kv, L.d.hidden, project, qrot, stage_bytes);
     int rc = ensure_scratch(ctx, sp.total);
@@ -1220,7 +1258,8 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         return fail(DKV_ERR_INVALID, "a paged pool is supported for attention over stored rows with a host-side length only");
 
     extend_prep_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, st>>>(
-        B, S_new, seqlen_past, n_past_blocks_dev, is_causal, row_map, L.d.row_stride, vseq, vrow, tok_pos, tok_slot);
+        B, S_new, seqlen_past, n_past_blocks_dev, is_causal, row_map, L.d.row_stride, vseq, vrow, tok_pos, tok_slot,
+        s_total_host, proj_to_stage ? cum : nullptr);
     DKV_CUDA(cudaGetLastError());
     ctx->launches += 1;
     if (!tensor_path) {
@@ -1234,10 +1273,23 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         DKV_CUDA(cudaGetLastError());
         ctx->launches += 1;
     }
+    uint4* stage_k = stage ? reinterpret_cast<uint4*>(base + sp.stage_k) : nullptr;
+    uint4* stage_v = stage ? reinterpret_cast<uint4*>(base + sp.stage_v) : nullptr;
     if (project) {
-        rc = launch_projection(ctx, L, X, static_cast<int>(rows), tok_pos, tok_slot, true, nullptr,
-                               reinterpret_cast<float*>(base + sp.splitk), st);
+        rc = launch_projection(ctx, L, X, static_cast<int>(rows), tok_pos, proj_to_stage ? cum : tok_slot, true, nullptr,
+                               reinterpret_cast<float*>(base + sp.splitk), st, false, proj_to_stage ? stage_k : nullptr,
+                               proj_to_stage ? stage_v : nullptr, static_cast<long long>(B) * s_total_host);
         if (rc != DKV_OK) return rc;
+        if (proj_to_stage) {
+            DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
+            DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+            unstage_rows_kernel<<<ctx->sm_count * 2, 256, 0, ctx->side>>>(
+                static_cast<uint4*>(L.k_dev), static_cast<uint4*>(L.v_dev), stage_k, stage_v, cum, tok_slot, rows, nh_kv * 16,
+                L.d.n_slots, ctx->status);
+            DKV_CUDA(cudaGetLastError());
+            DKV_CUDA(cudaEventRecord(ctx->ev_join, ctx->side));
+            ctx->launches += 1;
+        }
     }
     const __nv_bfloat16* q_use = static_cast<const __nv_bfloat16*>(Q);
     if (qrot) {
@@ -1264,12 +1316,12 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         const int32_t* ext_rows = row_map;
         long long ext_stride = L.d.row_stride;
         if (stage) {
-            uint4* ks = reinterpret_cast<uint4*>(base + sp.stage_k);
-            uint4* vs = reinterpret_cast<uint4*>(base + sp.stage_v);
+            uint4* ks = stage_k;
+            uint4* vs = stage_v;
             stage_rows_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(ks, vs, static_cast<const uint4*>(L.k_dev),
                                                                  static_cast<const uint4*>(L.v_dev), row_map,
                                                                  L.d.row_stride, B, s_total_host, nh_kv * 16, page_table,
-                                                                 pt_stride, L.page_shift);
+                                                                 pt_stride, L.page_shift, proj_to_stage ? seqlen_past : -1);
             DKV_CUDA(cudaGetLastError());
             ctx->launches += 1;
             const int64_t srows = static_cast<int64_t>(B) * s_total_host;
@@ -1309,6 +1361,7 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         }
         DKV_CUDA(cudaGetLastError());
         ctx->launches += 1;
+        if (proj_to_stage) DKV_CUDA(cudaStreamWaitEvent(st, ctx->ev_join, 0));   // the pool holds the new rows when the call's work is done
         return DKV_OK;
     }
     AttnParams ap{};
@@ -1553,16 +1606,35 @@ int dkv_extend_ragged(dkv_context* ctx, int layer_id, const void* X, const void*
     rc = ensure_scratch(ctx, sp.total);
     if (rc != DKV_OK) return rc;
     uint8_t* base = ctx->scratch;
+    uint4* ks = stage ? reinterpret_cast<uint4*>(base + sp.stage_k) : nullptr;
+    uint4* vs = stage ? reinterpret_cast<uint4*>(base + sp.stage_v) : nullptr;
+    // Host pool with projection: the new rows are projected straight into the staging copy, which the attention
+    // reads, and go to the host pool from there on the side stream while the attention runs - they cross the host
+    // link once, outside the critical path, instead of twice inside it.
+    const bool proj_to_stage = project && stage;
     if (project) {
         int* tok_pos = reinterpret_cast<int*>(base + sp.tok_pos);
         int* tok_slot = reinterpret_cast<int*>(base + sp.tok_slot);
-        extend_prep_ragged_kernel<<<static_cast<int>((T + 255) / 256), 256, 0, st>>>(B, static_cast<int>(T), dq0, dpast, drows,
-                                                                                  L.d.row_stride, tok_pos, tok_slot);
+        int* tok_pool_slot = reinterpret_cast<int*>(base + sp.vseq);
+        extend_prep_ragged_kernel<<<static_cast<int>((T + 255) / 256), 256, 0, st>>>(
+            B, static_cast<int>(T), dq0, dpast, drows, L.d.row_stride, proj_to_stage ? dkvoff : nullptr, tok_pos, tok_slot,
+            tok_pool_slot);
         DKV_CUDA(cudaGetLastError());
         ctx->launches += 1;
         rc = launch_projection(ctx, L, X, static_cast<int>(T), tok_pos, tok_slot, true, nullptr,
-                               reinterpret_cast<float*>(base + sp.splitk), st);
+                               reinterpret_cast<float*>(base + sp.splitk), st, false, proj_to_stage ? ks : nullptr,
+                               proj_to_stage ? vs : nullptr, kv_total);
         if (rc != DKV_OK) return rc;
+        if (proj_to_stage) {
+            DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
+            DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+            unstage_rows_kernel<<<ctx->sm_count * 2, 256, 0, ctx->side>>>(
+                static_cast<uint4*>(L.k_dev), static_cast<uint4*>(L.v_dev), ks, vs, tok_slot, tok_pool_slot, T, nh_kv * 16,
+                L.d.n_slots, ctx->status);
+            DKV_CUDA(cudaGetLastError());
+            DKV_CUDA(cudaEventRecord(ctx->ev_join, ctx->side));
+            ctx->launches += 1;
+        }
     }
     CUtensorMap tmQ, tmKs, tmVs;
     rc = encode_tile_map(&tmQ, Q, T, nh_q, G, TQ);
@@ -1570,12 +1642,10 @@ int dkv_extend_ragged(dkv_context* ctx, int layer_id, const void* X, const void*
     const CUtensorMap* tmK = &L.tmK_128;
     const CUtensorMap* tmV = &L.tmV_128;
     if (stage) {
-        uint4* ks = reinterpret_cast<uint4*>(base + sp.stage_k);
-        uint4* vs = reinterpret_cast<uint4*>(base + sp.stage_v);
         stage_rows_ragged_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(ks, vs, static_cast<const uint4*>(L.k_dev),
                                                                     static_cast<const uint4*>(L.v_dev), B, dkvoff, drows,
                                                                     L.d.row_stride, nh_kv * 16, page_table, pt_stride,
-                                                                    L.page_shift);
+                                                                    L.page_shift, proj_to_stage ? dpast : nullptr);
         DKV_CUDA(cudaGetLastError());
         ctx->launches += 1;
         if ((rc = encode_tile_map(&tmKs, ks, kv_total, nh_kv, 1, kExtTile)) != DKV_OK) return rc;
@@ -1602,6 +1672,7 @@ int dkv_extend_ragged(dkv_context* ctx, int layer_id, const void* X, const void*
     extend_attn_pp_kernel<<<grid, kPpThreads, kPpSmem, st>>>(tmQ, *tmK, *tmV, ep);
     DKV_CUDA(cudaGetLastError());
     ctx->launches += 1;
+    if (proj_to_stage) DKV_CUDA(cudaStreamWaitEvent(st, ctx->ev_join, 0));   // the pool holds the new rows when the call's work is done
     return DKV_OK;
 }
 
