@@ -1244,6 +1244,9 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
     // With a staging copy the new rows are projected straight into it (the attention reads them there) and reach
     // the host pool from the copy on the side stream, while the attention runs.
     const bool proj_to_stage = project && stage;
+    // Copy engines instead of SM loads/stores where the host knows the rows: request b in pool row b, contiguous.
+    const bool dma_rows = stage && !paged && L.pool_on_host && row_map == nullptr;
+    const size_t row_bytes = static_cast<size_t>(nh_kv) * 256;
     const size_t stage_bytes = stage ? static_cast<size_t>(B) * s_total_host * nh_kv * 256 : 0;
     ScratchPlan sp = plan_scratch(ctx, rows, nh_q, nh_kv, L.d.hidden, project, qrot, stage_bytes);
     int rc = ensure_scratch(ctx, sp.total);
@@ -1283,12 +1286,24 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         if (proj_to_stage) {
             DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
             DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
-            unstage_rows_kernel<<<ctx->sm_count * 2, 256, 0, ctx->side>>>(
-                static_cast<uint4*>(L.k_dev), static_cast<uint4*>(L.v_dev), stage_k, stage_v, cum, tok_slot, rows, nh_kv * 16,
-                L.d.n_slots, ctx->status);
-            DKV_CUDA(cudaGetLastError());
+            if (dma_rows) {
+                // Rows known on the host (request b lives in pool row b): one copy-engine transfer per request and tensor.
+                for (int b = 0; b < B; ++b) {
+                    const size_t src = (static_cast<size_t>(b) * s_total_host + seqlen_past) * row_bytes;
+                    const size_t dst = (static_cast<size_t>(b) * L.d.row_stride + seqlen_past) * row_bytes;
+                    DKV_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(L.d.k_pool) + dst, reinterpret_cast<uint8_t*>(stage_k) + src,
+                                             static_cast<size_t>(S_new) * row_bytes, cudaMemcpyDeviceToHost, ctx->side));
+                    DKV_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(L.d.v_pool) + dst, reinterpret_cast<uint8_t*>(stage_v) + src,
+                                             static_cast<size_t>(S_new) * row_bytes, cudaMemcpyDeviceToHost, ctx->side));
+                }
+            } else {
+                unstage_rows_kernel<<<ctx->sm_count * 2, 256, 0, ctx->side>>>(
+                    static_cast<uint4*>(L.k_dev), static_cast<uint4*>(L.v_dev), stage_k, stage_v, cum, tok_slot, rows, nh_kv * 16,
+                    L.d.n_slots, ctx->status);
+                DKV_CUDA(cudaGetLastError());
+                ctx->launches += 1;
+            }
             DKV_CUDA(cudaEventRecord(ctx->ev_join, ctx->side));
-            ctx->launches += 1;
         }
     }
     const __nv_bfloat16* q_use = static_cast<const __nv_bfloat16*>(Q);
@@ -1318,12 +1333,24 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         if (stage) {
             uint4* ks = stage_k;
             uint4* vs = stage_v;
-            stage_rows_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(ks, vs, static_cast<const uint4*>(L.k_dev),
-                                                                 static_cast<const uint4*>(L.v_dev), row_map,
-                                                                 L.d.row_stride, B, s_total_host, nh_kv * 16, page_table,
-                                                                 pt_stride, L.page_shift, proj_to_stage ? seqlen_past : -1);
-            DKV_CUDA(cudaGetLastError());
-            ctx->launches += 1;
+            if (dma_rows) {
+                const int n = proj_to_stage ? seqlen_past : s_total_host;
+                for (int b = 0; b < B && n > 0; ++b) {
+                    const size_t src = static_cast<size_t>(b) * L.d.row_stride * row_bytes;
+                    const size_t dst = static_cast<size_t>(b) * s_total_host * row_bytes;
+                    DKV_CUDA(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(ks) + dst, static_cast<const uint8_t*>(L.d.k_pool) + src,
+                                             static_cast<size_t>(n) * row_bytes, cudaMemcpyHostToDevice, st));
+                    DKV_CUDA(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(vs) + dst, static_cast<const uint8_t*>(L.d.v_pool) + src,
+                                             static_cast<size_t>(n) * row_bytes, cudaMemcpyHostToDevice, st));
+                }
+            } else {
+                stage_rows_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(ks, vs, static_cast<const uint4*>(L.k_dev),
+                                                                     static_cast<const uint4*>(L.v_dev), row_map,
+                                                                     L.d.row_stride, B, s_total_host, nh_kv * 16, page_table,
+                                                                     pt_stride, L.page_shift, proj_to_stage ? seqlen_past : -1);
+                DKV_CUDA(cudaGetLastError());
+                ctx->launches += 1;
+            }
             const int64_t srows = static_cast<int64_t>(B) * s_total_host;
             if ((rc = encode_tile_map(&tmKs, ks, srows, nh_kv, 1, kExtTile)) != DKV_OK) return rc;
             if ((rc = encode_tile_map(&tmVs, vs, srows, nh_kv, 1, kExtTile)) != DKV_OK) return rc;
@@ -1612,6 +1639,8 @@ int dkv_extend_ragged(dkv_context* ctx, int layer_id, const void* X, const void*
     // reads, and go to the host pool from there on the side stream while the attention runs - they cross the host
     // link once, outside the critical path, instead of twice inside it.
     const bool proj_to_stage = project && stage;
+    void* k_host = L.pool_on_host ? const_cast<void*>(static_cast<const void*>(L.d.k_pool)) : nullptr;   // host address of the pinned pool
+    void* v_host = L.pool_on_host ? const_cast<void*>(static_cast<const void*>(L.d.v_pool)) : nullptr;
     if (project) {
         int* tok_pos = reinterpret_cast<int*>(base + sp.tok_pos);
         int* tok_slot = reinterpret_cast<int*>(base + sp.tok_slot);
@@ -1628,12 +1657,18 @@ int dkv_extend_ragged(dkv_context* ctx, int layer_id, const void* X, const void*
         if (proj_to_stage) {
             DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
             DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
-            unstage_rows_kernel<<<ctx->sm_count * 2, 256, 0, ctx->side>>>(
-                static_cast<uint4*>(L.k_dev), static_cast<uint4*>(L.v_dev), ks, vs, tok_slot, tok_pool_slot, T, nh_kv * 16,
-                L.d.n_slots, ctx->status);
-            DKV_CUDA(cudaGetLastError());
+            // Contiguous rows: one copy-engine transfer per request and tensor (the faster way over the host link).
+            const size_t row_bytes = static_cast<size_t>(nh_kv) * 256;
+            for (int b = 0; b < B; ++b) {
+                const size_t src = (static_cast<size_t>(hkvoff[b]) + past_host[b]) * row_bytes;
+                const size_t dst = (static_cast<size_t>(rows_host[b]) * L.d.row_stride + past_host[b]) * row_bytes;
+                const size_t bytes = static_cast<size_t>(s_new_host[b]) * row_bytes;
+                DKV_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(k_host) + dst, reinterpret_cast<uint8_t*>(ks) + src, bytes,
+                                         cudaMemcpyDeviceToHost, ctx->side));
+                DKV_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(v_host) + dst, reinterpret_cast<uint8_t*>(vs) + src, bytes,
+                                         cudaMemcpyDeviceToHost, ctx->side));
+            }
             DKV_CUDA(cudaEventRecord(ctx->ev_join, ctx->side));
-            ctx->launches += 1;
         }
     }
     CUtensorMap tmQ, tmKs, tmVs;
@@ -1641,13 +1676,28 @@ int dkv_extend_ragged(dkv_context* ctx, int layer_id, const void* X, const void*
     if (rc != DKV_OK) return rc;
     const CUtensorMap* tmK = &L.tmK_128;
     const CUtensorMap* tmV = &L.tmV_128;
-    if (stage) {
+    if (stage && !paged && k_host != nullptr) {
+        // Contiguous rows of a host pool: the copy engines bring them in (55.6 against 51.5 GB/s for SM reads).
+        const size_t row_bytes = static_cast<size_t>(nh_kv) * 256;
+        for (int b = 0; b < B; ++b) {
+            const int n = proj_to_stage ? past_host[b] : past_host[b] + s_new_host[b];
+            if (n == 0) continue;
+            const size_t src = static_cast<size_t>(rows_host[b]) * L.d.row_stride * row_bytes;
+            const size_t dst = static_cast<size_t>(hkvoff[b]) * row_bytes;
+            DKV_CUDA(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(ks) + dst, static_cast<const uint8_t*>(k_host) + src,
+                                     static_cast<size_t>(n) * row_bytes, cudaMemcpyHostToDevice, st));
+            DKV_CUDA(cudaMemcpyAsync(reinterpret_cast<uint8_t*>(vs) + dst, static_cast<const uint8_t*>(v_host) + src,
+                                     static_cast<size_t>(n) * row_bytes, cudaMemcpyHostToDevice, st));
+        }
+    } else if (stage) {
         stage_rows_ragged_kernel<<<ctx->sm_count * 8, 256, 0, st>>>(ks, vs, static_cast<const uint4*>(L.k_dev),
                                                                     static_cast<const uint4*>(L.v_dev), B, dkvoff, drows,
                                                                     L.d.row_stride, nh_kv * 16, page_table, pt_stride,
                                                                     L.page_shift, proj_to_stage ? dpast : nullptr);
         DKV_CUDA(cudaGetLastError());
         ctx->launches += 1;
+    }
+    if (stage) {                     // the attention reads the staging copy
         if ((rc = encode_tile_map(&tmKs, ks, kv_total, nh_kv, 1, kExtTile)) != DKV_OK) return rc;
         if ((rc = encode_tile_map(&tmVs, vs, kv_total, nh_kv, 1, kExtTile)) != DKV_OK) return rc;
         tmK = &tmKs;
