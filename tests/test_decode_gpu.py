@@ -336,6 +336,24 @@ def test_randomised_configurations(seed):
         ctx.set("proj_decode", -1)
 
 
+@pytest.mark.parametrize("nh_q,nh_kv,host", [(8, 8, True), (8, 2, False), (8, 2, True), (16, 1, False)])
+def test_results_do_not_depend_on_scheduling(nh_q, nh_kv, host):
+    """Static split of the tiles over warps, fixed-order split-K sums and merges: repeated runs give the same bits
+    (output and stored K/V)."""
+    shape = _shape(1024, nh_q, nh_kv)
+    lens = [1500, 37, 800, 2, 4097, 333]
+    case = workloads.make_decode_case(shape, lens, 16, 41, DEV, kv_on_host=host)
+    kernel.register_layer(91, case["k_pool"], case["v_pool"], case["wk"], case["wv"], case["cos_sin"], page_size=16)
+    outs = []
+    for _ in range(4):
+        outs.append(kernel.decode(91, case["q"], case["seq_lens"], shape.scale, page_table=case["page_table"],
+                                  x=case["x"]).clone())
+        torch.cuda.synchronize()
+    get_context(0).raise_on_status()
+    kernel.unregister_layer(91)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+
+
 def test_errors():
     with pytest.raises(RuntimeError, match="not registered"):
         kernel.decode(999, torch.zeros(1, 128, dtype=torch.bfloat16, device=DEV),

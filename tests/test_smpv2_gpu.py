@@ -319,6 +319,17 @@ def test_extend_ragged_attend_paged():
         kernel.extend_ragged(74, None, Q.to(DEV), [1], [0], [0], SCALE)
 
 
+def test_extend_is_reproducible():
+    X, Wk, Wv, Q, K, V, cs = _rand_case(1, 8, 2, 900, 200, 512, seed=71)
+    outs = []
+    for _ in range(3):
+        Kd, Vd = K.clone().to(DEV), V.clone().to(DEV)
+        outs.append(kernel.smpv2_fwd(X.to(DEV), Wk.to(DEV), Wv.to(DEV), Q.to(DEV), Kd, Vd, cs.to(DEV), SCALE, True, 200, -1).clone())
+        torch.cuda.synchronize()
+    get_context(0).raise_on_status()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
 def test_extend_paths_agree():
     """The tensor-core extend kernel and the row-streamed path (decode kernels, one virtual request per new
     row) implement the same function: compare them directly, non-causal included."""
