@@ -92,12 +92,16 @@ except Exception:  # ImportError, or a broken install
 
 
 def pinned_zeros(shape, dtype: torch.dtype) -> torch.Tensor:
-    """Zero-filled page-locked host tensor.
+    """Zero-filled page-locked host tensor, placed in the memory of the socket the current CUDA device hangs off
+    where the machine has more than one (directkv_b200/numa.py; a no-op elsewhere).
 
     Without a CUDA driver nothing can be page-locked; then a pageable tensor is returned so the
     host-side logic (indexing, free-list) can still be exercised.  The engine itself refuses
     pageable pools (the C ABI checks the pointer's memory type).
     """
     if torch.cuda.is_available():
-        return torch.zeros(shape, dtype=dtype, pin_memory=True)
+        from .numa import local_to_gpu
+
+        with local_to_gpu(torch.cuda.current_device()):
+            return torch.zeros(shape, dtype=dtype, pin_memory=True)
     return torch.zeros(shape, dtype=dtype)
