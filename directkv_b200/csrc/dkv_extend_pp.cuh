@@ -98,9 +98,10 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     for (int g = 0; g < 2; ++g) {
         int kv_end = p.is_causal ? past + q0 + (g + 1) * TQ : s_total;
         if (kv_end > s_total) kv_end = s_total;
-        n_half[g] = (kv_end + kPpHalf - 1) / kPpHalf;         // n_half[1] >= n_half[0] >= 1
+        n_half[g] = (kv_end + kPpHalf - 1) / kPpHalf;         // n_half[1] >= n_half[0] >= 1 ...
+        if (q0 + g * TQ >= s_new) n_half[g] = 0;              // ... unless tile 1 lies past the last new row: it does nothing
     }
-    const int n_max = (n_half[1] + 1) >> 1;                   // K/V tiles to load
+    const int n_max = ((n_half[1] > n_half[0] ? n_half[1] : n_half[0]) + 1) >> 1;   // K/V tiles to load
 
     if (tid == 0) {
         mbar_init(&ctl->bar_q, 1);
@@ -213,7 +214,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 umma_commit(&ctl->bar_o[g][t & 1]);
                 if (((t & 1) || t == n_g - 1) && !PP_MODE(4)) umma_commit(&ctl->empty[slot]);
             };
-            if (ok) issue_qk(0);
+            if (ok && n_g > 0) issue_qk(0);
             if (ok && n_g > 1) issue_qk(1);
             for (int t = 0; ok && t < n_g; ++t) {
                 PP_T0(tw);
@@ -373,7 +374,9 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             PP_ACC(1, tc);
         }
 
-        if (ok) {
+        if (n_g == 0) {
+            ok = true;           // an empty tile: nothing to wait for, nothing to store
+        } else if (ok) {
             // The last two products (one per P buffer) end the accumulation.
             if (n_g >= 2)
                 ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_o[g][(n_g - 2) & 1], ((n_g - 2) >> 1) & 1) && !ctl->abort);
@@ -383,7 +386,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (!ok) {
             if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
             ctl->abort = 1;
-        } else {
+        } else if (n_g > 0) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const bool store = my_tok < s_new;
             __nv_bfloat16* dst = p.out + ((static_cast<long long>(q_row0) + (store ? my_tok : 0)) * p.nh_q + qhead0 + row % G) * 128;

@@ -67,7 +67,7 @@ def test_projection_full_hidden_with_rope(H):
     _run_fwd(X, Wk, Wv, Q, K, V, cs, True, 24)
 
 
-@pytest.mark.parametrize("S_new,S_past", [(1, 0), (1, 333), (130, 0), (257, 70), (64, 64)])
+@pytest.mark.parametrize("S_new,S_past", [(1, 0), (1, 333), (130, 0), (257, 70), (64, 64), (32, 500), (33, 96), (96, 31)])
 def test_unaligned_lengths_gqa(S_new, S_past):
     X, Wk, Wv, Q, K, V, cs = _rand_case(2, 8, 2, S_new, S_past, 256, seed=7 + S_new)
     _run_fwd(X, Wk, Wv, Q, K, V, cs, True, S_past)
