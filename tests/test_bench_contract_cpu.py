@@ -27,3 +27,23 @@ def test_reference_arm_other_ranks_exit_quietly():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2"],
                          capture_output=True, text=True, timeout=120, cwd=ROOT, env=env)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_longctx_csv_has_the_reference_columns(tmp_path):
+    """benchmarks/bench_offload_longctx.py:65-71 in the reference."""
+    import csv
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("bench_mod", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench.LONGCTX_CSV_HEADER == [
+        "system", "model", "seq_length", "mean_latency_s", "p50_latency_s", "p90_latency_s", "p99_latency_s",
+        "mean_e2e_latency_s", "p50_e2e_latency_s", "p90_e2e_latency_s", "p99_e2e_latency_s", "gpu_memory_peak_mb",
+        "memory_saving_pct", "throughput_tps"]
+    path = tmp_path / "fig11.csv"
+    bench.write_longctx_csv(str(path), [{"system": "s", "model": "m", "seq_length": 32768, "mean_latency_s": 0.085}])
+    bench.write_longctx_csv(str(path), [{"system": "s", "model": "m", "seq_length": 131072, "mean_latency_s": 0.334}])
+    rows = list(csv.DictReader(open(path)))
+    assert [r["seq_length"] for r in rows] == ["32768", "131072"] and rows[0]["p99_e2e_latency_s"] == ""
+    assert bench._pct([5, 1, 3], 0.5) == 3 and bench._pct([1.0], 0.99) == 1.0
