@@ -33,12 +33,21 @@
 #define PP_DECL unsigned long long pp_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
 #define PP_FLUSH do { if (lane == 0 && p.timing) for (int i_ = 0; i_ < 8; ++i_) if (pp_acc[i_]) atomicAdd(p.timing + i_, pp_acc[i_]); } while (0)
 #define PP_MODE(m) ((p.dbg_mode & (m)) != 0)
+#ifdef DKV_PP_TIMING_ISSUER
+#define PP_ACC_S(idx, var)
+#define PP_ACC_I(idx, var) PP_ACC(idx, var)
+#else
+#define PP_ACC_S(idx, var) PP_ACC(idx, var)
+#define PP_ACC_I(idx, var)
+#endif
 #else
 #define PP_MODE(m) false
 #define PP_DECL
 #define PP_FLUSH
 #define PP_T0(var)
 #define PP_ACC(idx, var)
+#define PP_ACC_S(idx, var)
+#define PP_ACC_I(idx, var)
 #define PP_CNT(idx)
 #endif
 
@@ -100,6 +109,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (kv_end > s_total) kv_end = s_total;
         n_half[g] = (kv_end + kPpHalf - 1) / kPpHalf;         // n_half[1] >= n_half[0] >= 1 ...
         if (q0 + g * TQ >= s_new) n_half[g] = 0;              // ... unless tile 1 lies past the last new row: it does nothing
+        if (PP_MODE(8) && g == 1) n_half[g] = 0;
     }
     const int n_max = ((n_half[1] > n_half[0] ? n_half[1] : n_half[0]) + 1) >> 1;   // K/V tiles to load
 
@@ -178,11 +188,13 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             int ring_ready = -1;                              // highest ring sequence number known to have landed
             auto wait_ring = [&](int q) {
                 if (PP_MODE(4)) return;
+                PP_T0(t_wr);
                 while (ok && ring_ready < q) {
                     const int nq = ring_ready + 1;
                     ok = mbar_wait_bounded(&ctl->full[nq % kPpSlots], (nq / kPpSlots) & 1);
                     ring_ready = nq;
                 }
+                PP_ACC(4, t_wr);
             };
             auto issue_qk = [&](int t) {                      // S[t & 1] = Q K(rows 64 (t & 1) ... of tile t >> 1)^T
                 const int q = 2 * (t >> 1), slot = q % kPpSlots;
@@ -191,6 +203,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tc_fence_after_sync();
                 const uint64_t kd = k_desc0 + static_cast<uint64_t>((slot * kExtTileBytes + (t & 1) * kPpHalf * 128) >> 4);
                 const uint32_t d = tS + (t & 1) * kPpHalf;
+                PP_T0(t_a);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     if (PP_MODE(2)) break;
@@ -198,8 +211,11 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     const uint64_t off = static_cast<uint64_t>(((k >> 2) * kExtHalfBytes + (k & 3) * 32) / unit);
                     umma_bf16_ss(d, q_desc + off, kd + off, idesc_qk, k > 0 ? 1u : 0u);
                 }
+                PP_ACC_I(2, t_a);
+                PP_T0(t_b);
                 umma_commit(&ctl->bar_s[g][t & 1]);
                 if (((t & 1) || t == n_g - 1) && !PP_MODE(4)) umma_commit(&ctl->empty[slot]);   // this tile's last read of K(t >> 1)
+                PP_ACC_I(1, t_b);
             };
             auto issue_pv = [&](int t) {                      // O (+)= P[t & 1] V(rows 64 (t & 1) ... of tile t >> 1)
                 const int q = 2 * (t >> 1) + 1, slot = q % kPpSlots;
@@ -208,11 +224,15 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tc_fence_after_sync();
                 const uint64_t vd = v_desc0 + static_cast<uint64_t>((slot * kExtTileBytes + (t & 1) * kPpHalf * 128) >> 4);
                 const uint32_t pa = tS + (t & 1) * kPpHalf;   // P lies over the S buffer it came from
+                PP_T0(t_a);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)                   // 16 keys per step = 8 packed columns of P, 16 rows of V
                     if (!PP_MODE(2)) umma_bf16_ts(tO, pa + k * 8, vd + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
+                PP_ACC_I(0, t_a);
+                PP_T0(t_b);
                 umma_commit(&ctl->bar_o[g][t & 1]);
                 if (((t & 1) || t == n_g - 1) && !PP_MODE(4)) umma_commit(&ctl->empty[slot]);
+                PP_ACC_I(1, t_b);
             };
             if (ok && n_g > 0) issue_qk(0);
             if (ok && n_g > 1) issue_qk(1);
@@ -222,8 +242,10 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 PP_ACC(3, tw);
                 if (!ok) break;
                 tc_fence_after_sync();
+                PP_T0(t_is);
                 issue_pv(t);                                  // reads P(t) before the next product overwrites the buffer
                 if (ok && t + 2 < n_g) issue_qk(t + 2);
+                PP_ACC(6, t_is);
             }
             // Tiles the other query tile still reads: every ring slot expects one arrival from each issuer.
             for (int q = 2 * ((n_g + 1) >> 1); ok && q < 2 * n_max; ++q) {
@@ -258,7 +280,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             // S(t) complete; the product that wrote it was issued after P V(t - 2), so that one has read the buffer.
             PP_T0(ts);
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_s[g][bf], (t >> 1) & 1) && !ctl->abort);
-            PP_ACC(0, ts);
+            PP_ACC_S(0, ts);
             PP_CNT(7);
             PP_T0(tc);
             if (!ok) break;
@@ -274,12 +296,9 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 continue;
             }
             uint32_t r0[32], r1[32];                          // the row's 64 scores stay in registers
-            PP_T0(t_ld);
             tmem_ld_32x32(tSb, r0);
             tmem_ld_32x32(tSb + 32, r1);
             tmem_ld_wait();
-            PP_ACC(4, t_ld);
-            PP_T0(t_mx);
             float m_tile = -INFINITY;
             if (masked) {
 #pragma unroll
@@ -288,19 +307,22 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     if (col0 + 32 + i <= my_limit) m_tile = fmaxf(m_tile, __uint_as_float(r1[i]) * p.scale_log2);
                 }
             } else {
-                float a0 = -INFINITY, a1 = -INFINITY;
+                float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;     // four short chains
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    a0 = fmaxf(a0, __uint_as_float(r0[i]));
-                    a1 = fmaxf(a1, __uint_as_float(r1[i]));
+                for (int i = 0; i < 16; i += 2) {
+                    a0 = fmax3(a0, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
+                    a1 = fmax3(a1, __uint_as_float(r0[16 + i]), __uint_as_float(r0[17 + i]));
+                    a2 = fmax3(a2, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
+                    a3 = fmax3(a3, __uint_as_float(r1[16 + i]), __uint_as_float(r1[17 + i]));
                 }
+                a0 = fmaxf(a0, a2);
+                a1 = fmaxf(a1, a3);
                 m_tile = fmaxf(a0, a1) * p.scale_log2;            // scale_log2 > 0 on this path
             }
             // Move the reference maximum only when the true one is more than the step above it (warp-uniform):
             // then O and l are rescaled; otherwise probabilities are formed against the old reference (<= 2^8).
             const bool grow = (m_tile > m_used + kPpRescaleStep) || (m_used == -INFINITY);
             const bool any_grow = __any_sync(0xffffffffu, grow);
-            PP_ACC(6, t_mx);
             if (any_grow) {
                 float m_to = fmaxf(m_used, m_tile);
                 if (m_to == -INFINITY) m_to = 0.f;
@@ -328,28 +350,41 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             PP_T0(t_ex);
             const float neg_m = -m_used;
             uint32_t pk[32];
-            float s4[4] = {0.f, 0.f, 0.f, 0.f};
+            // In place and in phases (scale and shift, exponentials, mask, sums and packing), so that each phase is a
+            // run of independent instructions on one pipe.
+            const uint64_t sc2 = f32x2(p.scale_log2, p.scale_log2), nm2 = f32x2(neg_m, neg_m);
+            float* x0 = reinterpret_cast<float*>(r0);
+            float* x1 = reinterpret_cast<float*>(r1);
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
-                float e0 = ex2_approx(fmaf(__uint_as_float(r0[i]), p.scale_log2, neg_m));
-                float e1 = ex2_approx(fmaf(__uint_as_float(r0[i + 1]), p.scale_log2, neg_m));
-                float e2 = ex2_approx(fmaf(__uint_as_float(r1[i]), p.scale_log2, neg_m));
-                float e3 = ex2_approx(fmaf(__uint_as_float(r1[i + 1]), p.scale_log2, neg_m));
-                if (masked) {
-                    if (col0 + i > my_limit) e0 = 0.f;
-                    if (col0 + i + 1 > my_limit) e1 = 0.f;
-                    if (col0 + 32 + i > my_limit) e2 = 0.f;
-                    if (col0 + 32 + i + 1 > my_limit) e3 = 0.f;
-                }
-                s4[0] += e0;
-                s4[1] += e1;
-                s4[2] += e2;
-                s4[3] += e3;
-                pk[i >> 1] = pack_bf16x2_alu(e0, e1);
-                pk[16 + (i >> 1)] = pack_bf16x2_alu(e2, e3);
+                f32x2_split(fma_f32x2(f32x2(x0[i], x0[i + 1]), sc2, nm2), x0[i], x0[i + 1]);
+                f32x2_split(fma_f32x2(f32x2(x1[i], x1[i + 1]), sc2, nm2), x1[i], x1[i + 1]);
             }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                x0[i] = ex2_approx(x0[i]);
+                x1[i] = ex2_approx(x1[i]);
+            }
+            if (masked) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (col0 + i > my_limit) x0[i] = 0.f;
+                    if (col0 + 32 + i > my_limit) x1[i] = 0.f;
+                }
+            }
+            uint64_t sa = f32x2(0.f, 0.f), sb = sa;
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                sa = add_f32x2(sa, f32x2(x0[i], x0[i + 1]));
+                sb = add_f32x2(sb, f32x2(x1[i], x1[i + 1]));
+                pk[i >> 1] = pack_bf16x2(x0[i], x0[i + 1]);
+                pk[16 + (i >> 1)] = pack_bf16x2(x1[i], x1[i + 1]);
+            }
+            float s4[4];
+            f32x2_split(sa, s4[0], s4[1]);
+            f32x2_split(sb, s4[2], s4[3]);
             const float psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-            PP_ACC(2, t_ex);
+            PP_ACC_S(2, t_ex);
             tmem_st_32x32(tSb, pk);
             tmem_st_wait();
             l += psum;
@@ -371,7 +406,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->bar_p[g][bf]);
-            PP_ACC(1, tc);
+            PP_ACC_S(1, tc);
         }
 
         if (n_g == 0) {
