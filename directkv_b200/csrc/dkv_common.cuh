@@ -171,6 +171,27 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return d;
 }
 
+// 2^x for a packed pair on the FMA and integer pipes, for softmax arguments (x <= ~8): round to the nearest integer
+// n with the 1.5 * 2^23 trick, cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, below bf16 rounding), n
+// added into the exponent field.  Takes load off the special-function unit, which does 4 ex2 per cycle and scheduler.
+__device__ __forceinline__ uint64_t ex2_poly_f32x2(uint64_t x) {
+    float a, b;
+    f32x2_split(x, a, b);
+    x = f32x2(fmaxf(a, -126.f), fmaxf(b, -126.f));
+    const uint64_t magic = f32x2(12582912.f, 12582912.f), neg_magic = f32x2(-12582912.f, -12582912.f);
+    const uint64_t xr = add_f32x2(x, magic);
+    const uint64_t n = add_f32x2(xr, neg_magic);
+    const uint64_t f = fma_f32x2(n, f32x2(-1.f, -1.f), x);
+    uint64_t q = fma_f32x2(f, f32x2(0.05517166769f, 0.05517166769f), f32x2(0.24261112209f, 0.24261112209f));
+    q = fma_f32x2(q, f, f32x2(0.69326098571f, 0.69326098571f));
+    q = fma_f32x2(q, f, f32x2(0.99992807355f, 0.99992807355f));
+    float q0, q1, r0, r1;
+    f32x2_split(q, q0, q1);
+    f32x2_split(xr, r0, r1);
+    return f32x2(__uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23)),
+                 __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23)));
+}
+
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 // ---------------------------------------------------------------------------

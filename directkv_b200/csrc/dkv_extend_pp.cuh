@@ -7,7 +7,8 @@
 // tiles and specialises its warps:
 //
 //   warp 0      TMA producer: both Q tiles once, then K(0), V(0), K(1), V(1), ... through a ring of 32 KB slots
-//   warps 1, 2  MMA issuers (one thread each): S_g = Q_g K^T and O_g += P_g V for tile g = 0 / 1
+//   warps 1, 2  MMA issuers (one thread each): S_g = Q_g K^T for tile g = 0 / 1
+//   warps 3, 12 MMA issuers (one thread each): O_g += P_g V for tile g = 0 / 1
 //   warps 4-7   softmax of tile 0 (thread = query row = TMEM lane)
 //   warps 8-11  softmax of tile 1
 //
@@ -54,10 +55,14 @@
 namespace dkv {
 
 constexpr int kPpSlots = 5;                                   // ring of [128 x 128] bf16 tiles: K and V alternate
-constexpr int kPpThreads = 384;
+constexpr int kPpThreads = 416;                               // 13 warps: producer, 4 issuers, 2 x 4 softmax
 constexpr int kPpSmem = 2 * kExtTileBytes /*Q0,Q1*/ + kPpSlots * kExtTileBytes + 256 + 1024;
 constexpr float kPpRescaleStep = 8.f;                         // log2 units the maximum may lag behind
 constexpr int kPpHalf = 64;                                   // keys per half-tile
+#ifndef DKV_PP_POLY_MASK
+#define DKV_PP_POLY_MASK 6
+#endif
+constexpr int kPpPolyMask = DKV_PP_POLY_MASK;                 // pairs i with (i & mask) == mask go to the FMA pipe: 6 = every fourth (measured best), 2 = every second, 0x40 = none
 
 struct PpCtrl {
     uint64_t bar_q;
@@ -117,7 +122,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         mbar_init(&ctl->bar_q, 1);
         for (int s = 0; s < kPpSlots; ++s) {
             mbar_init(&ctl->full[s], 1);
-            mbar_init(&ctl->empty[s], 2);                     // one arrival per MMA issuer
+            mbar_init(&ctl->empty[s], 2);                     // one arrival per query tile (the issuer that reads the slot)
         }
         for (int g = 0; g < 2; ++g)
             for (int bf = 0; bf < 2; ++bf) {
@@ -152,7 +157,6 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 tma_load_3d(sQ + g * kExtTileBytes + kExtHalfBytes, &tmQ, &ctl->bar_q, 64, qhead0, q_row0 + q0 + g * TQ);
             }
             for (int q = 0; q < 2 * n_max; ++q) {             // q even: K(q/2), odd: V(q/2)
-                if (PP_MODE(4)) break;
                 const int s = q % kPpSlots;
                 PP_T0(tp);
                 if (q >= kPpSlots && !mbar_wait_bounded(&ctl->empty[s], ((q / kPpSlots) - 1) & 1)) {
@@ -172,38 +176,33 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
         __syncwarp();
     } else if (warp == 1 || warp == 2) {
-        // ------------------------------------------------ MMA issuers ------------------------------------------------
-        // One thread per query tile (warp 1: tile 0, warp 2: tile 1), so neither tile waits for the other's
-        // handshakes.  Descriptors are built once; inside the loops only constants are added to them.
+        // ------------------------------------------------ MMA issuers: S = Q K^T ------------------------------------------------
+        // One thread per query tile and product (warps 1, 2: S of tile 0 / 1; warps 3, 12: P V of tile 0 / 1).  A
+        // tcgen05.mma blocks its thread while the pipe is busy and every commit and wait costs it another hundred
+        // cycles or so, so the fewer steps a thread has per half-tile, the less the pipe idles.  Descriptors are built
+        // once; inside the loops only constants are added to them.
         if (lane == 0) {
             const int g = warp - 1;
             const int n_g = n_half[g];
             constexpr uint32_t idesc_qk = umma_idesc_bf16_f32(kExtTile, kPpHalf);
-            constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(kExtTile, kExtTile) | (1u << 16);   // B (V) is MN-major
             const uint64_t q_desc = umma_desc_k_sw128(smem_u32(sQ + g * kExtTileBytes));
             const uint64_t k_desc0 = umma_desc_k_sw128(smem_u32(sRing));
-            const uint64_t v_desc0 = umma_desc_mn_sw128(smem_u32(sRing), kExtHalfBytes);
-            const uint32_t tS = tmem_base + g * 128, tO = tmem_base + 256 + g * 128;
+            const uint32_t tS = tmem_base + g * 128;
             bool ok = mbar_wait_bounded(&ctl->bar_q, 0);
-            int ring_ready = -1;                              // highest ring sequence number known to have landed
-            auto wait_ring = [&](int q) {
-                if (PP_MODE(4)) return;
-                PP_T0(t_wr);
-                while (ok && ring_ready < q) {
-                    const int nq = ring_ready + 1;
-                    ok = mbar_wait_bounded(&ctl->full[nq % kPpSlots], (nq / kPpSlots) & 1);
-                    ring_ready = nq;
-                }
-                PP_ACC(4, t_wr);
-            };
-            auto issue_qk = [&](int t) {                      // S[t & 1] = Q K(rows 64 (t & 1) ... of tile t >> 1)^T
+            for (int t = 0; ok && t < n_g; ++t) {
                 const int q = 2 * (t >> 1), slot = q % kPpSlots;
-                wait_ring(q);
-                if (!ok) return;
+                PP_T0(tw);
+                // Buffer t & 1 holds P(t - 2) until the product that reads it is complete (another thread issues it).
+                if (t >= 2) ok = mbar_wait_bounded(&ctl->bar_o[g][t & 1], ((t - 2) >> 1) & 1) && !ctl->abort;
+                PP_ACC(3, tw);
+                PP_T0(t_wr);
+                if (ok && !(t & 1)) ok = mbar_wait_bounded(&ctl->full[slot], (q / kPpSlots) & 1);
+                PP_ACC(4, t_wr);
+                if (!ok) break;
                 tc_fence_after_sync();
+                PP_T0(t_is);
                 const uint64_t kd = k_desc0 + static_cast<uint64_t>((slot * kExtTileBytes + (t & 1) * kPpHalf * 128) >> 4);
                 const uint32_t d = tS + (t & 1) * kPpHalf;
-                PP_T0(t_a);
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     if (PP_MODE(2)) break;
@@ -211,46 +210,46 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                     const uint64_t off = static_cast<uint64_t>(((k >> 2) * kExtHalfBytes + (k & 3) * 32) / unit);
                     umma_bf16_ss(d, q_desc + off, kd + off, idesc_qk, k > 0 ? 1u : 0u);
                 }
-                PP_ACC_I(2, t_a);
-                PP_T0(t_b);
                 umma_commit(&ctl->bar_s[g][t & 1]);
-                if (((t & 1) || t == n_g - 1) && !PP_MODE(4)) umma_commit(&ctl->empty[slot]);   // this tile's last read of K(t >> 1)
-                PP_ACC_I(1, t_b);
-            };
-            auto issue_pv = [&](int t) {                      // O (+)= P[t & 1] V(rows 64 (t & 1) ... of tile t >> 1)
+                if ((t & 1) || t == n_g - 1) umma_commit(&ctl->empty[slot]);   // this tile's last read of K(t >> 1)
+                PP_ACC(6, t_is);
+            }
+            // K tiles the other query tile still reads: every ring slot expects one arrival per query tile.
+            for (int q = 2 * ((n_g + 1) >> 1); ok && q < 2 * n_max; q += 2) {
+                ok = mbar_wait_bounded(&ctl->full[q % kPpSlots], (q / kPpSlots) & 1);
+                if (ok) mbar_arrive(&ctl->empty[q % kPpSlots]);
+            }
+            if (!ok) {
+                atomicOr(p.status, kStatusWaitTimeout);
+                ctl->abort = 1;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 3 || warp == 12) {
+        // ------------------------------------------------ MMA issuers: O += P V ------------------------------------------------
+        if (lane == 0) {
+            const int g = warp == 3 ? 0 : 1;
+            const int n_g = n_half[g];
+            constexpr uint32_t idesc_pv = umma_idesc_bf16_f32(kExtTile, kExtTile) | (1u << 16);   // B (V) is MN-major
+            const uint64_t v_desc0 = umma_desc_mn_sw128(smem_u32(sRing), kExtHalfBytes);
+            const uint32_t tS = tmem_base + g * 128, tO = tmem_base + 256 + g * 128;
+            bool ok = true;
+            for (int t = 0; ok && t < n_g; ++t) {
                 const int q = 2 * (t >> 1) + 1, slot = q % kPpSlots;
-                wait_ring(q);
-                if (!ok) return;
+                ok = mbar_wait_bounded(&ctl->bar_p[g][t & 1], (t >> 1) & 1) && !ctl->abort;
+                if (ok && !(t & 1)) ok = mbar_wait_bounded(&ctl->full[slot], (q / kPpSlots) & 1);
+                if (!ok) break;
                 tc_fence_after_sync();
                 const uint64_t vd = v_desc0 + static_cast<uint64_t>((slot * kExtTileBytes + (t & 1) * kPpHalf * 128) >> 4);
                 const uint32_t pa = tS + (t & 1) * kPpHalf;   // P lies over the S buffer it came from
-                PP_T0(t_a);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)                   // 16 keys per step = 8 packed columns of P, 16 rows of V
                     if (!PP_MODE(2)) umma_bf16_ts(tO, pa + k * 8, vd + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
-                PP_ACC_I(0, t_a);
-                PP_T0(t_b);
                 umma_commit(&ctl->bar_o[g][t & 1]);
-                if (((t & 1) || t == n_g - 1) && !PP_MODE(4)) umma_commit(&ctl->empty[slot]);
-                PP_ACC_I(1, t_b);
-            };
-            if (ok && n_g > 0) issue_qk(0);
-            if (ok && n_g > 1) issue_qk(1);
-            for (int t = 0; ok && t < n_g; ++t) {
-                PP_T0(tw);
-                ok = mbar_wait_bounded(&ctl->bar_p[g][t & 1], (t >> 1) & 1) && !ctl->abort;
-                PP_ACC(3, tw);
-                if (!ok) break;
-                tc_fence_after_sync();
-                PP_T0(t_is);
-                issue_pv(t);                                  // reads P(t) before the next product overwrites the buffer
-                if (ok && t + 2 < n_g) issue_qk(t + 2);
-                PP_ACC(6, t_is);
+                if ((t & 1) || t == n_g - 1) umma_commit(&ctl->empty[slot]);
             }
-            // Tiles the other query tile still reads: every ring slot expects one arrival from each issuer.
-            for (int q = 2 * ((n_g + 1) >> 1); ok && q < 2 * n_max; ++q) {
-                if (PP_MODE(4)) break;
-                wait_ring(q);
+            for (int q = 2 * ((n_g + 1) >> 1) + 1; ok && q < 2 * n_max; q += 2) {
+                ok = mbar_wait_bounded(&ctl->full[q % kPpSlots], (q / kPpSlots) & 1);
                 if (ok) mbar_arrive(&ctl->empty[q % kPpSlots]);
             }
             if (!ok) {
@@ -261,7 +260,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         __syncwarp();
     }
 
-    if (warp >= 4) {
+    if (warp >= 4 && warp < 12) {
         // ------------------------------------------------ softmax groups ------------------------------------------------
         const int g = (warp - 4) >> 2;                        // query tile of this warp
         const int row = ((warp & 3) << 5) + lane;             // TMEM lane == query row of the tile
@@ -277,7 +276,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
         for (int t = 0; t < n_g; ++t) {
             const int bf = t & 1;
-            // S(t) complete; the product that wrote it was issued after P V(t - 2), so that one has read the buffer.
+            // S(t) complete; the product that wrote it was issued after P V(t - 2) had completed and read the buffer.
             PP_T0(ts);
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_s[g][bf], (t >> 1) & 1) && !ctl->abort);
             PP_ACC_S(0, ts);
@@ -361,9 +360,16 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 f32x2_split(fma_f32x2(f32x2(x1[i], x1[i + 1]), sc2, nm2), x1[i], x1[i + 1]);
             }
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                x0[i] = ex2_approx(x0[i]);
-                x1[i] = ex2_approx(x1[i]);
+            for (int i = 0; i < 32; i += 2) {
+                if ((i & kPpPolyMask) == kPpPolyMask) {       // this pair on the FMA pipe
+                    f32x2_split(ex2_poly_f32x2(f32x2(x0[i], x0[i + 1])), x0[i], x0[i + 1]);
+                    f32x2_split(ex2_poly_f32x2(f32x2(x1[i], x1[i + 1])), x1[i], x1[i + 1]);
+                } else {
+                    x0[i] = ex2_approx(x0[i]);
+                    x0[i + 1] = ex2_approx(x0[i + 1]);
+                    x1[i] = ex2_approx(x1[i]);
+                    x1[i + 1] = ex2_approx(x1[i + 1]);
+                }
             }
             if (masked) {
 #pragma unroll
