@@ -47,8 +47,28 @@ struct AttnParams {
     long long row_stride;          // contiguous mode: slots per pool row
     int n_new;                     // trailing tokens per request that are NOT read from the pool
     int total_warps;               // gridDim.x * warps per CTA of the partial kernel
+    int min_units;                 // fewest (head-slot, tile) units a warp takes (>= 1)
     float scale_log2;              // softmax scale * log2(e)
 };
+
+// Units per warp of the streaming grid.  A short step (one 4K request: 2048 units for 2368 warps) would give every
+// warp a single tile and the merge one record per tile; with a floor the work goes to fewer warps, which are taken
+// one per CTA in turn (sm_spread) so that the rows still come through all SMs' load paths.
+struct WarpSplit {
+    long long qn;
+    bool spread;
+};
+__device__ __forceinline__ WarpSplit warp_split(const AttnParams& p, long long U) {
+    WarpSplit w;
+    w.qn = (U + p.total_warps - 1) / p.total_warps;
+    w.spread = w.qn < p.min_units;
+    if (w.spread) w.qn = p.min_units;
+    return w;
+}
+// Logical index (position of the warp's unit range, and of its partial record) of a physical warp.
+__device__ __forceinline__ int logical_warp(const WarpSplit& w, int cta, int warp, int nwarps, int nctas) {
+    return w.spread ? warp * nctas + cta : cta * nwarps + warp;
+}
 
 // ---------------------------------------------------------------------------
 // prep: tiles per request -> exclusive prefix sum; with n_new == 1 also the position and the
@@ -211,8 +231,9 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 
     const int nhs = p.nh_kv * p.nsub;
     const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
-    const long long qn = (U + p.total_warps - 1) / p.total_warps;
-    const int gw = blockIdx.x * NWARPS + warp;
+    const WarpSplit ws = warp_split(p, U);
+    const long long qn = ws.qn;
+    const int gw = logical_warp(ws, blockIdx.x, warp, NWARPS, gridDim.x);
     const long long u0 = static_cast<long long>(gw) * qn;
     const long long u1 = (u0 + qn < U) ? u0 + qn : U;
     if (u0 >= u1) return;  // warps are independent: no CTA-wide barrier follows
@@ -459,7 +480,7 @@ __global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const MergePa
     const int tiles_b = p.cum_tiles[b + 1] - p.cum_tiles[b];
     if (row_valid && tiles_b > 0) {
         const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
-        const long long qn = (U + p.total_warps - 1) / p.total_warps;
+        const long long qn = warp_split(p, U).qn;
         const long long s0 = static_cast<long long>(p.cum_tiles[b]) * nhs + static_cast<long long>(hs) * tiles_b;
         const long long e0 = s0 + tiles_b;
         const int seg = b * nhs + hs;

@@ -98,8 +98,9 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const bool hi_rows = G > 8;
     const int nhs = p.nh_kv * p.nsub;
     const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
-    const long long qn = (U + p.total_warps - 1) / p.total_warps;
-    const int gw = blockIdx.x * NWARPS + warp;
+    const WarpSplit ws = warp_split(p, U);
+    const long long qn = ws.qn;
+    const int gw = logical_warp(ws, blockIdx.x, warp, NWARPS, gridDim.x);
     const long long u0 = static_cast<long long>(gw) * qn;
     const long long u1 = (u0 + qn < U) ? u0 + qn : U;
     if (u0 >= u1) return;
@@ -332,8 +333,9 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     const int G = p.g_total / p.nsub;                 // query heads per record, <= 8
     const int nhs = p.nh_kv * p.nsub;
     const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
-    const long long qn = (U + p.total_warps - 1) / p.total_warps;
-    const int gw = blockIdx.x * NWARPS + warp;
+    const WarpSplit ws = warp_split(p, U);
+    const long long qn = ws.qn;
+    const int gw = logical_warp(ws, blockIdx.x, warp, NWARPS, gridDim.x);
     const long long u0 = static_cast<long long>(gw) * qn;
     const long long u1 = (u0 + qn < U) ? u0 + qn : U;
     if (u0 >= u1) return;

@@ -142,6 +142,7 @@ struct dkv_context {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     int attn_variant = -1;              // -1: chosen per call from the head grouping
     int attn_ctas = 0;
+    int attn_min_units = 8;          // HBM pools: fewest (head-slot, tile) units per warp of the streaming grid
     int proj_split_k = 0;
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
     int proj_wide = 1;                  // 256-token projection tiles when there are more 128-token tiles than SMs
@@ -728,6 +729,8 @@ int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool
     const int ctas = attn_cta_count(ctx);
     const int mma_variant = ctx->attn_variant < 0 ? 2 : ctx->attn_variant;
     ap.total_warps = ctas * (mma ? kVarWarps[mma_variant] : variant_warps(ctx, G));
+    // Rows in host memory want every warp's loads in flight; rows in HBM want few partial records on short steps.
+    ap.min_units = (L.pool_on_host || ctx->attn_min_units < 1) ? 1 : ctx->attn_min_units;
     const CUtensorMap& tmK = mma ? (paged ? L.tmK_sw_page : L.tmK_sw_16) : (paged ? L.tmK_page : L.tmK_16);
     const CUtensorMap& tmV = mma ? (paged ? L.tmV_sw_page : L.tmV_sw_16) : (paged ? L.tmV_page : L.tmV_16);
     cudaError_t e;
@@ -889,6 +892,9 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
         ctx->wait_limit_ms = value;
     } else if (!strcmp(key, "profile_attn")) {
         ctx->profile_attn = value ? 1 : 0;
+    } else if (!strcmp(key, "attn_min_units")) {
+        DKV_REQUIRE(value >= 1 && value <= 64, "attn_min_units must be 1..64");
+        ctx->attn_min_units = static_cast<int>(value);
     } else if (!strcmp(key, "proj_split_k")) {
         DKV_REQUIRE(value >= 0 && value <= 256, "proj_split_k out of range");
         ctx->proj_split_k = value;

@@ -235,6 +235,7 @@ extern "C" int dkv_decode_noalloc(const dkv_noalloc_args* a, void* stream) {
     ap.row_stride = 0;
     ap.n_new = 0;
     ap.total_warps = ctas * warps;
+    ap.min_units = 1;
     ap.scale_log2 = a->softmax_scale * 1.4426950408889634f;
 
     if (G == 4)

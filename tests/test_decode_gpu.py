@@ -284,11 +284,14 @@ def test_dma_staged_decode_matches_streaming():
     rm = torch.tensor(rows, dtype=torch.int32, device=DEV)
     outs, pools = [], []
     # The copy lives in HBM, where four query heads per KV head would pick the tensor-core form of the streaming
-    # kernel; with it switched off both runs execute the same arithmetic in the same order.
+    # kernel and short steps give each warp several tiles; with both switched off the two runs execute the same
+    # arithmetic in the same order.
     get_context(0).set("attn_mma", 0)
+    get_context(0).set("attn_min_units", 1)
     for staged in (False, True, True):
         if len(outs) == 2:
             get_context(0).set("attn_mma", -1)
+            get_context(0).set("attn_min_units", 8)
         Kp, Vp = K.clone().pin_memory(), V.clone().pin_memory()
         kernel.register_layer(81, Kp, Vp, wk, wv, cs, row_stride=s_pad)
         if staged:
