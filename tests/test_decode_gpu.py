@@ -357,6 +357,22 @@ def test_results_do_not_depend_on_scheduling(nh_q, nh_kv, host):
     assert all(torch.equal(outs[0], o) for o in outs[1:])
 
 
+@pytest.mark.parametrize("nh_q,nh_kv", [(4, 4), (8, 2), (16, 1)])
+def test_units_per_warp_floor(nh_q, nh_kv):
+    """Pools in HBM: a floor on the tiles a warp takes (short steps leave fewer partial records).  Every floor, from
+    none to one that leaves a handful of warps with work, gives the oracle's result."""
+    ctx = get_context(0)
+    outs = []
+    try:
+        for floor in (1, 3, 8, 64):
+            ctx.set("attn_min_units", floor)
+            outs.append(_run_decode(_shape(512, nh_q, nh_kv), [700, 33, 1, 2049], 16, cfg_id=55, kv_on_host=False))
+    finally:
+        ctx.set("attn_min_units", 8)
+    for o in outs[1:]:
+        assert (o.float() - outs[0].float()).abs().max().item() < 1e-2
+
+
 def test_errors():
     with pytest.raises(RuntimeError, match="not registered"):
         kernel.decode(999, torch.zeros(1, 128, dtype=torch.bfloat16, device=DEV),
