@@ -31,6 +31,8 @@ STATUS_BITS = {
     1 << 1: "a write-back slot was outside the KV pool",
     1 << 2: "a RoPE position was outside the cos/sin table",
     1 << 3: "the tensor-core completion barrier ran out of time",
+    1 << 4: "the sequence-split exchange found a record of another step (the ranks' calls do not line up)",
+    1 << 5: "a sequence length or row led outside the page table",
 }
 
 PARTIAL_STRIDE = 132  # floats per unnormalised partial row: O[128], m (log2 domain), l, 2 pad
@@ -78,6 +80,7 @@ class DecodeArgs(C.Structure):
         ("src_page_table", C.c_void_p),
         ("src_pt_stride", C.c_int),
         ("src_row_map", C.c_void_p),
+        ("pt_rows", C.c_int),
     ]
 
 
@@ -102,6 +105,7 @@ class NoAllocArgs(C.Structure):
         ("sync_and_check", C.c_int),
         ("err_buf", C.c_char_p),
         ("err_buf_len", C.c_int),
+        ("status_out", C.c_void_p),
     ]
 
 

@@ -42,6 +42,7 @@ struct AttnParams {
     int g_total;                   // NH_q / NH_kv
     int nsub;                      // g_total / G: q-head sub-groups that re-read the same KV
     int pt_stride;
+    int pt_rows;                   // rows of the page table, or 0 when the caller did not say (row not checked)
     int page_size, page_shift;     // power of two (paged mode)
     int rows_per_box;              // min(16, page_size): rows one TMA box brings
     long long row_stride;          // contiguous mode: slots per pool row
@@ -85,9 +86,10 @@ struct PrepParams {
     const int* page_table;
     const int* row_map;
     const int* pos_offset;    // [batch] added to the RoPE position, or nullptr
-    int pt_stride, page_size, page_shift;
+    int pt_stride, pt_rows, page_size, page_shift;   // pt_rows: rows of the page table, 0 = not given
     long long row_stride;
     int save;
+    unsigned int* status;     // receives kStatusBadPage when the new token's page lies outside the table
 };
 
 __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams pp) {
@@ -108,11 +110,15 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams pp) {
                 long long slot = -1;
                 if (pp.save && pos >= 0) {
                     const int row = pp.row_map ? pp.row_map[b] : b;
-                    if (pp.page_table)
-                        slot = (static_cast<long long>(
-                                    pp.page_table[static_cast<long long>(row) * pp.pt_stride + (pos >> pp.page_shift)])
-                                << pp.page_shift) + (pos & (pp.page_size - 1));
-                    else
+                    if (pp.page_table) {
+                        const int pg = pos >> pp.page_shift;
+                        if (pg >= pp.pt_stride || row < 0 || (pp.pt_rows > 0 && row >= pp.pt_rows)) {
+                            if (pp.status != nullptr) atomicOr(pp.status, kStatusBadPage);   // the token is not stored
+                        } else {
+                            slot = (static_cast<long long>(pp.page_table[static_cast<long long>(row) * pp.pt_stride + pg])
+                                    << pp.page_shift) + (pos & (pp.page_size - 1));
+                        }
+                    } else
                         slot = static_cast<long long>(row) * pp.row_stride + pos;
                 }
                 pp.tok_pos[b] = pos + (pp.pos_offset ? pp.pos_offset[b] : 0);
@@ -167,6 +173,19 @@ struct TileCursor {
     }
 };
 
+// Page-table entry (row, pg) with both indices held inside the table.  seq_lens and row_map are device data that
+// no host code has seen: a length beyond pt_stride pages, or a row beyond the table, is reported in the status
+// word and the nearest entry is read instead (wrong rows for that request, but no access outside the table).
+__device__ __forceinline__ int page_at(const AttnParams& p, int row, int pg) {
+    const bool bad = pg >= p.pt_stride || row < 0 || (p.pt_rows > 0 && row >= p.pt_rows);
+    if (bad) {
+        atomicOr(p.status, kStatusBadPage);
+        pg = pg < p.pt_stride ? pg : p.pt_stride - 1;
+        row = row < 0 ? 0 : (p.pt_rows > 0 && row >= p.pt_rows) ? p.pt_rows - 1 : row;
+    }
+    return p.page_table[static_cast<long long>(row) * p.pt_stride + pg];
+}
+
 // Lane 0 only: start the TMA copies of one tile into a stage.
 __device__ __forceinline__ void issue_tile(const AttnParams& p, const CUtensorMap* tmK, const CUtensorMap* tmV,
                                            const TileCursor& c, uint8_t* stage, uint64_t* bar) {
@@ -179,7 +198,7 @@ __device__ __forceinline__ void issue_tile(const AttnParams& p, const CUtensorMa
         tma_load_3d(stage, tmK, bar, 0, h, static_cast<int>(slot0));
         tma_load_3d(stage + kTileBytes, tmV, bar, 0, h, static_cast<int>(slot0));
     } else if (p.page_size >= kTileTokens) {
-        const int page = p.page_table[static_cast<long long>(row) * p.pt_stride + (tok0 >> p.page_shift)];
+        const int page = page_at(p, row, tok0 >> p.page_shift);
         const long long slot0 = (static_cast<long long>(page) << p.page_shift) + (tok0 & (p.page_size - 1));
         mbar_arrive_expect_tx(bar, kStageBytes);
         tma_load_3d(stage, tmK, bar, 0, h, static_cast<int>(slot0));
@@ -191,9 +210,9 @@ __device__ __forceinline__ void issue_tile(const AttnParams& p, const CUtensorMa
         const int max_pages = kTileTokens >> p.page_shift;
         npages = npages < max_pages ? npages : max_pages;
         mbar_arrive_expect_tx(bar, static_cast<uint32_t>(npages * rows * kRowBytes * 2));
-        const int* pt = p.page_table + static_cast<long long>(row) * p.pt_stride + (tok0 >> p.page_shift);
+        const int pg0 = tok0 >> p.page_shift;
         for (int r = 0; r < npages; ++r) {
-            const long long slot0 = static_cast<long long>(pt[r]) << p.page_shift;
+            const long long slot0 = static_cast<long long>(page_at(p, row, pg0 + r)) << p.page_shift;
             tma_load_3d(stage + r * rows * kRowBytes, tmK, bar, 0, h, static_cast<int>(slot0));
             tma_load_3d(stage + kTileBytes + r * rows * kRowBytes, tmV, bar, 0, h, static_cast<int>(slot0));
         }
@@ -445,12 +464,15 @@ struct MergeParams {
     float* part_out;                 // [B, NH_q, kPartialStride] unnormalised partial, or nullptr
     // Sequence split without a collective call: the unnormalised record of every row is stored into the
     // exchange buffer of EVERY rank (plain stores over NVLink for peers) at [x_rank][row], then one
-    // system-scope increment per row tells that rank how many rows of x_rank have landed.
+    // system-scope increment per row tells that rank how many rows of x_rank have landed.  The host passes
+    // the half of each rank's double buffer (records and counters) that belongs to this step's parity, and the
+    // step's sequence number, which travels in every record so that the consumer can tell a stale one.
     int x_world;                     // 0: off
     int x_rank;
+    unsigned int x_tag;              // sequence number of the step (never 0)
     long long x_max_rows;
-    float* x_part[kMaxExchangeRanks];            // rank p's buffer [x_world, x_max_rows, kPartialStride]
-    unsigned int* x_count[kMaxExchangeRanks];    // rank p's arrival counters [x_world]
+    float* x_part[kMaxExchangeRanks];            // rank p's buffer of this parity [x_world, x_max_rows, kPartialStride]
+    unsigned int* x_count[kMaxExchangeRanks];    // rank p's arrival counters of this parity [x_world]
 };
 
 // WPR warps share one (request, query head) row: each takes blocks of 8 consecutive partial records (loads
@@ -580,7 +602,7 @@ __global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const MergePa
         for (int r = 0; r < mp.x_world; ++r) {
             float* po = mp.x_part[r] + (static_cast<long long>(mp.x_rank) * mp.x_max_rows + row) * kPartialStride;
             *reinterpret_cast<float4*>(po + 4 * lane) = acc;
-            if (lane == 0) *reinterpret_cast<float2*>(po + 128) = make_float2(m, l);
+            if (lane == 0) *reinterpret_cast<float4*>(po + 128) = make_float4(m, l, __uint_as_float(mp.x_tag), 0.f);
         }
         __threadfence_system();      // the record is visible system-wide before the count moves
         __syncwarp();
@@ -637,9 +659,10 @@ __global__ void __launch_bounds__(128) merge_rank_partials_kernel(const float* _
 // its records for this step have landed in THIS GPU's buffer, then merges them from local memory.
 // ---------------------------------------------------------------------------
 struct ExchangeMergeParams {
-    const float* parts;                       // this rank's buffer [world, max_rows, kPartialStride]
-    const unsigned int* count;                // this rank's arrival counters [world]
-    unsigned int expected[kMaxExchangeRanks]; // cumulative rows each rank must have delivered
+    const float* parts;                       // this rank's buffer of the step's parity [world, max_rows, kPartialStride]
+    const unsigned int* count;                // this rank's arrival counters of that parity [world]
+    unsigned int expected[kMaxExchangeRanks]; // cumulative rows each rank must have delivered on that parity
+    unsigned int tag;                         // sequence number every record of this step carries
     int world;
     long long max_rows, rows;
     __nv_bfloat16* out;                       // [rows, 128]
@@ -681,10 +704,12 @@ __global__ void __launch_bounds__(128) merge_exchange_kernel(const ExchangeMerge
     }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float m = -INFINITY, l = 0.f;
+    bool stale = false;
     for (int k = 0; k < ep.world; ++k) {
         const float* rec = ep.parts + (static_cast<long long>(k) * ep.max_rows + r) * kPartialStride;
-        const float2 ml = __ldcg(reinterpret_cast<const float2*>(rec + 128));
+        const float4 ml = __ldcg(reinterpret_cast<const float4*>(rec + 128));
         const float4 oi = __ldcg(reinterpret_cast<const float4*>(rec + 4 * lane));
+        stale |= (__float_as_uint(ml.z) != ep.tag);      // a record of another step: the ranks' calls do not line up
         const float mn = fmaxf(m, ml.x);
         const float mu = (mn == -INFINITY) ? 0.f : mn;
         const float a = exp2f(m - mu), c = exp2f(ml.x - mu);
@@ -695,6 +720,7 @@ __global__ void __launch_bounds__(128) merge_exchange_kernel(const ExchangeMerge
         l = l * a + ml.y * c;
         m = mn;
     }
+    if (stale && lane == 0) atomicOr(ep.status, kStatusExchangeOrder);
     const float inv = l > 0.f ? 1.f / l : 0.f;
     uint2 w;
     w.x = pack_bf16x2(acc.x * inv, acc.y * inv);

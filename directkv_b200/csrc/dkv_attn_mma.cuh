@@ -69,7 +69,7 @@ __device__ __forceinline__ void issue_tile_sw(const AttnParams& p, const CUtenso
         mbar_arrive_expect_tx(bar, kStageBytes);
         four(0, static_cast<int>(static_cast<long long>(row) * p.row_stride + tok0));
     } else if (p.page_size >= kTileTokens) {
-        const int page = p.page_table[static_cast<long long>(row) * p.pt_stride + (tok0 >> p.page_shift)];
+        const int page = page_at(p, row, tok0 >> p.page_shift);
         mbar_arrive_expect_tx(bar, kStageBytes);
         four(0, static_cast<int>((static_cast<long long>(page) << p.page_shift) + (tok0 & (p.page_size - 1))));
     } else {
@@ -79,8 +79,9 @@ __device__ __forceinline__ void issue_tile_sw(const AttnParams& p, const CUtenso
         const int max_pages = kTileTokens >> p.page_shift;
         npages = npages < max_pages ? npages : max_pages;
         mbar_arrive_expect_tx(bar, static_cast<uint32_t>(npages * rows * kRowBytes * 2));
-        const int* pt = p.page_table + static_cast<long long>(row) * p.pt_stride + (tok0 >> p.page_shift);
-        for (int r = 0; r < npages; ++r) four(r * rows, static_cast<int>(static_cast<long long>(pt[r]) << p.page_shift));
+        const int pg0 = tok0 >> p.page_shift;
+        for (int r = 0; r < npages; ++r)
+            four(r * rows, static_cast<int>(static_cast<long long>(page_at(p, row, pg0 + r)) << p.page_shift));
     }
 }
 

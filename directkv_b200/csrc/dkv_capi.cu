@@ -130,11 +130,21 @@ constexpr int kMaxCounters = 4096;
 
 }  // namespace
 
+// A device buffer that grows on demand.  Launches recorded by a stream capture keep the address they were given
+// for as long as the graph lives, so a buffer that a capture has seen is never freed before the context is
+// destroyed: when it has to grow, the old allocation is retired instead.
+struct DevBuffer {
+    uint8_t* ptr = nullptr;
+    size_t bytes = 0;
+    bool in_graph = false;              // a stream capture recorded launches that point into this allocation
+};
+
 struct dkv_context {
     int device = 0;
     int sm_count = 0;
-    uint8_t* scratch = nullptr;
-    size_t scratch_bytes = 0;
+    DevBuffer scratch;                  // per-call tables, partial records, new-token rows, split-K slices
+    DevBuffer stage;                    // extend over a host or paged pool: the requests' rows gathered in HBM
+    std::vector<void*> retired;         // outgrown allocations that a captured graph may still use
     unsigned int* status = nullptr;     // device status word
     unsigned int* counters = nullptr;   // split-K arrival counters, zero between launches
     std::map<int, LayerState> layers;
@@ -169,12 +179,17 @@ struct dkv_exchange {
     dkv_context* ctx = nullptr;
     int rank = 0, world = 0;
     long long max_rows = 0;
-    uint8_t* local = nullptr;                       // cudaMalloc: records [world, max_rows, 132] fp32, then counters
+    // cudaMalloc: records [2, world, max_rows, 132] fp32, then counters [2, kMaxExchangeRanks].  The leading 2 is
+    // the parity of the step: consecutive steps use different halves, so a rank that runs one step ahead of a
+    // peer (it cannot be further ahead, see dkv_decode_exchange) never stores over records the peer still reads.
+    uint8_t* local = nullptr;
     size_t part_bytes = 0;
+    size_t half_floats = 0;                                  // floats of one parity half of the record area
     float* part[dkv::kMaxExchangeRanks] = {nullptr};         // every rank's record area, as mapped into this process
     unsigned int* count[dkv::kMaxExchangeRanks] = {nullptr}; // every rank's arrival counters
     void* opened[dkv::kMaxExchangeRanks] = {nullptr};        // IPC mappings to close
-    unsigned int expected[dkv::kMaxExchangeRanks] = {0};     // rows each rank has delivered so far (cumulative)
+    unsigned int expected[2][dkv::kMaxExchangeRanks] = {{0}}; // rows each rank has delivered so far, per parity (cumulative)
+    unsigned long long steps = 0;                            // calls of dkv_decode_exchange so far
 };
 
 namespace {
@@ -480,7 +495,8 @@ constexpr size_t kProjSmem = static_cast<size_t>(kProjStages) * kProjStage + 409
 size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
 
 struct ScratchPlan {
-    size_t cum, tok_pos, tok_slot, vseq, vrow, partials, kv_new, splitk, q_rot, stage_k, stage_v, total;
+    size_t cum, tok_pos, tok_slot, vseq, vrow, partials, kv_new, splitk, q_rot, total;   // offsets into ctx->scratch
+    size_t stage_k, stage_v, stage_total;                                                // offsets into ctx->stage
 };
 
 // The tensor-core form reads 128-byte row segments (two 64-column swizzled boxes per row); over PCIe those make
@@ -589,27 +605,55 @@ ScratchPlan plan_scratch(const dkv_context* ctx, int64_t rows, int nh_q, int nh_
     }
     s.q_rot = off;
     if (with_qrot) off += align256(static_cast<size_t>(rows) * nh_q * 128 * 2);
-    off = (off + 1023) & ~static_cast<size_t>(1023);
-    s.stage_k = off;
-    off += align256(stage_bytes);
-    s.stage_v = off;
-    off += align256(stage_bytes);
     s.total = off;
+    s.stage_k = 0;
+    s.stage_v = (stage_bytes + 1023) & ~static_cast<size_t>(1023);      // TMA bases: keep both halves 1 KB aligned
+    s.stage_total = stage_bytes ? 2 * s.stage_v : 0;
     return s;
 }
 
-int ensure_scratch(dkv_context* ctx, size_t bytes) {
-    if (bytes <= ctx->scratch_bytes) return DKV_OK;
-    uint8_t* p = nullptr;
-    const size_t want = bytes + (bytes >> 2);
-    DKV_CUDA(cudaMalloc(&p, want));
-    if (ctx->scratch) {
-        DKV_CUDA(cudaDeviceSynchronize());
-        DKV_CUDA(cudaFree(ctx->scratch));
+bool stream_is_capturing(cudaStream_t st) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess) {
+        (void)cudaGetLastError();       // e.g. the legacy stream while another stream captures: not our capture
+        return false;
     }
-    ctx->scratch = p;
-    ctx->scratch_bytes = want;
+    return cap != cudaStreamCaptureStatusNone;
+}
+
+// Makes `b` hold at least `bytes`.  `capturing`: the calling entry point is being recorded into a CUDA graph.
+// Growth never happens under capture (the caller must have reserved), and an allocation that any capture has
+// seen is retired, not freed, so a later replay of that graph still finds its memory.
+int ensure_buffer(dkv_context* ctx, DevBuffer* b, size_t bytes, bool capturing, const char* what) {
+    if (bytes > b->bytes) {
+        if (capturing)
+            return fail(DKV_ERR_UNSUPPORTED,
+                        "%s of %zu bytes needed during stream capture but %zu are reserved: size it before capturing "
+                        "(dkv_context_reserve, or one eager call of the same shape)", what, bytes, b->bytes);
+        uint8_t* p = nullptr;
+        const size_t want = bytes + (bytes >> 2);
+        DKV_CUDA(cudaMalloc(&p, want));
+        if (b->ptr != nullptr) {
+            if (b->in_graph) {
+                ctx->retired.push_back(b->ptr);
+            } else {
+                DKV_CUDA(cudaDeviceSynchronize());      // launches in flight may still use the old allocation
+                DKV_CUDA(cudaFree(b->ptr));
+            }
+        }
+        b->ptr = p;
+        b->bytes = want;
+        b->in_graph = false;
+    }
+    if (capturing) b->in_graph = true;
     return DKV_OK;
+}
+
+int ensure_scratch(dkv_context* ctx, const ScratchPlan& sp, cudaStream_t st) {
+    const bool capturing = stream_is_capturing(st);
+    int rc = ensure_buffer(ctx, &ctx->scratch, sp.total, capturing, "scratch");
+    if (rc != DKV_OK || sp.stage_total == 0) return rc;
+    return ensure_buffer(ctx, &ctx->stage, sp.stage_total, capturing, "staging memory");
 }
 
 int device_pointer_of(void* p, void** out, const char* what) {
@@ -629,6 +673,9 @@ int device_pointer_of(void* p, void** out, const char* what) {
 int build_layer(LayerState* L, const dkv_layer_desc* d) {
     DKV_REQUIRE(d->k_pool && d->v_pool, "k_pool / v_pool must not be NULL");
     DKV_REQUIRE(d->n_slots > 0 && d->nh_kv > 0, "n_slots and nh_kv must be positive");
+    // Slot numbers travel as 32-bit TMA coordinates and int32 page-table entries.
+    DKV_REQUIRE(d->n_slots <= static_cast<int64_t>(INT32_MAX), "n_slots (%lld) exceeds the 2^31 - 1 slots a pool can address",
+                (long long)d->n_slots);
     DKV_REQUIRE(d->page_size >= 1 && (d->page_size & (d->page_size - 1)) == 0, "page_size (%d) must be a power of two",
                 d->page_size);
     DKV_REQUIRE((reinterpret_cast<uintptr_t>(d->k_pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(d->v_pool) & 15) == 0,
@@ -664,14 +711,6 @@ int build_layer(LayerState* L, const dkv_layer_desc* d) {
     if (d->cos_sin) DKV_REQUIRE(d->max_pos > 0, "max_pos must be positive when cos_sin is given");
     return DKV_OK;
 }
-
-#ifdef DKV_PP_TIMING
-unsigned long long* pp_timing_buffer() {
-    static unsigned long long* buf = nullptr;
-    if (!buf && (cudaMalloc(&buf, 64) != cudaSuccess || cudaMemset(buf, 0, 64) != cudaSuccess)) buf = nullptr;
-    return buf;
-}
-#endif
 
 // Projection of T rows of X with RoPE and write-back (tcgen05 kernel).
 int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int T, const int* tok_pos,
@@ -847,7 +886,9 @@ int dkv_context_destroy(dkv_context* ctx) {
     if (ctx->side) cudaStreamDestroy(ctx->side);
     if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
     if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
-    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->scratch.ptr) cudaFree(ctx->scratch.ptr);
+    if (ctx->stage.ptr) cudaFree(ctx->stage.ptr);
+    for (void* p : ctx->retired) cudaFree(p);
     if (ctx->ragged_host) cudaFreeHost(ctx->ragged_host);
     if (ctx->ragged_dev) cudaFree(ctx->ragged_dev);
     if (ctx->ev_ragged) cudaEventDestroy(ctx->ev_ragged);
@@ -862,7 +903,7 @@ int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv,
     DKV_REQUIRE(max_rows > 0 && nh_q > 0 && nh_kv > 0 && nh_q % nh_kv == 0, "bad reserve sizes");
     DKV_CUDA(cudaSetDevice(ctx->device));
     ScratchPlan s = plan_scratch(ctx, max_rows, nh_q, nh_kv, hidden, hidden > 0, true);
-    return ensure_scratch(ctx, s.total);
+    return ensure_buffer(ctx, &ctx->scratch, s.total, false, "scratch");
 }
 
 int dkv_context_set(dkv_context* ctx, const char* key, int value) {
@@ -973,7 +1014,7 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
         DKV_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & 7) == 0, "out must be 8-byte aligned");
     }
     const bool paged = a->page_table != nullptr;
-    if (paged) DKV_REQUIRE(a->pt_stride > 0, "pt_stride must be positive");
+    if (paged) DKV_REQUIRE(a->pt_stride > 0 && a->pt_rows >= 0, "pt_stride must be positive and pt_rows >= 0");
     else DKV_REQUIRE(L.d.row_stride > 0, "layer was registered without row_stride; pass a page_table");
     DKV_REQUIRE(a->new_mode >= DKV_NEW_NONE && a->new_mode <= DKV_NEW_GIVEN, "bad new_mode %d", a->new_mode);
     if (a->new_mode == DKV_NEW_PROJECT) {
@@ -986,9 +1027,9 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
 
     const bool with_proj = a->new_mode == DKV_NEW_PROJECT;
     ScratchPlan sp = plan_scratch(ctx, a->batch, a->nh_q, nh_kv, L.d.hidden, with_proj, false);
-    int rc = ensure_scratch(ctx, sp.total);
+    int rc = ensure_scratch(ctx, sp, st);
     if (rc != DKV_OK) return rc;
-    uint8_t* base = ctx->scratch;
+    uint8_t* base = ctx->scratch.ptr;
     int* cum = reinterpret_cast<int*>(base + sp.cum);
     int* tok_pos = reinterpret_cast<int*>(base + sp.tok_pos);
     int* tok_slot = reinterpret_cast<int*>(base + sp.tok_slot);
@@ -1006,6 +1047,8 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
     prep.row_map = a->row_map;
     prep.pos_offset = a->pos_offset;
     prep.pt_stride = a->pt_stride;
+    prep.pt_rows = a->pt_rows;
+    prep.status = ctx->status;
     prep.page_size = L.d.page_size;
     prep.page_shift = L.page_shift;
     prep.row_stride = L.d.row_stride;
@@ -1053,6 +1096,7 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
     ap.page_table = a->page_table;
     ap.row_map = a->row_map;
     ap.pt_stride = a->pt_stride;
+    ap.pt_rows = a->pt_rows;
     if (a->kv_source_layer != 0) {
         auto its = ctx->layers.find(a->kv_source_layer);
         if (its == ctx->layers.end())
@@ -1065,6 +1109,7 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
         ap.page_table = a->src_page_table;
         ap.row_map = a->src_row_map;
         ap.pt_stride = a->src_pt_stride;
+        ap.pt_rows = 0;
     }
     ap.seq_lens = a->seq_lens;
     ap.cum_tiles = cum;
@@ -1087,28 +1132,18 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
     mp.lse = a->lse_out;
     mp.part_out = a->partial_out;
     if (ex != nullptr) {
+        const int parity = static_cast<int>(ex->steps & 1ull);
         mp.x_world = ex->world;
         mp.x_rank = ex->rank;
+        mp.x_tag = static_cast<unsigned int>(ex->steps % 0xfffffffeull) + 1u;
         mp.x_max_rows = ex->max_rows;
         for (int r = 0; r < ex->world; ++r) {
-            mp.x_part[r] = ex->part[r];
-            mp.x_count[r] = ex->count[r];
+            mp.x_part[r] = ex->part[r] + parity * ex->half_floats;
+            mp.x_count[r] = ex->count[r] + parity * kMaxExchangeRanks;
         }
     }
     return launch_attention(ctx, *Lsrc, ap, src_paged, mp, st, a->new_mode == DKV_NEW_PROJECT ? ctx->ev_join : nullptr);
 }
-
-#ifdef DKV_PP_TIMING
-// Instrumented builds only: cycle counters of extend_attn_pp_kernel (see the PP_ACC indices in dkv_extend_pp.cuh).
-extern "C" int dkv_debug_pp_timing(unsigned long long* out8, int reset) {
-    unsigned long long* d = pp_timing_buffer();
-    if (!d) return DKV_ERR_CUDA;
-    if (cudaDeviceSynchronize() != cudaSuccess) return DKV_ERR_CUDA;
-    if (out8 && cudaMemcpy(out8, d, 64, cudaMemcpyDeviceToHost) != cudaSuccess) return DKV_ERR_CUDA;
-    if (reset && cudaMemset(d, 0, 64) != cudaSuccess) return DKV_ERR_CUDA;
-    return DKV_OK;
-}
-#endif
 
 int dkv_decode(dkv_context* ctx, const dkv_decode_args* a, void* stream) { return decode_impl(ctx, a, stream, nullptr); }
 
@@ -1123,7 +1158,8 @@ int dkv_exchange_create(dkv_context* ctx, int rank, int world, int64_t max_rows,
     ex->rank = rank;
     ex->world = world;
     ex->max_rows = max_rows;
-    ex->part_bytes = align256(static_cast<size_t>(world) * max_rows * kPartialStride * sizeof(float));
+    ex->half_floats = static_cast<size_t>(world) * max_rows * kPartialStride;
+    ex->part_bytes = align256(2 * ex->half_floats * sizeof(float));
     cudaError_t e = cudaMalloc(&ex->local, ex->part_bytes + 256);
     if (e == cudaSuccess) e = cudaMemset(ex->local, 0, ex->part_bytes + 256);
     if (e != cudaSuccess) {
@@ -1200,13 +1236,21 @@ int dkv_decode_exchange(dkv_context* ctx, dkv_exchange* ex, const dkv_decode_arg
     local.lse_out = nullptr;
     int rc = decode_impl(ctx, &local, stream, ex);
     if (rc != DKV_OK) return rc;
+    // Why two halves are enough: a rank's consumer kernel of step n runs after its own producer of step n (same
+    // stream), and returns only when every rank's step-n records have landed here.  So when rank A issues stores
+    // of step n+1, every rank has finished PRODUCING step n, and A has finished consuming it; a slower rank B may
+    // still be consuming step n - from the half of parity n, which A's step-n+1 stores do not touch.  A cannot
+    // reach step n+2 before B has produced step n+1, which B does only after its step-n consumer.
+    const int parity = static_cast<int>(ex->steps & 1ull);
     ExchangeMergeParams ep{};
-    ep.parts = ex->part[ex->rank];
-    ep.count = ex->count[ex->rank];
+    ep.parts = ex->part[ex->rank] + parity * ex->half_floats;
+    ep.count = ex->count[ex->rank] + parity * kMaxExchangeRanks;
+    ep.tag = static_cast<unsigned int>(ex->steps % 0xfffffffeull) + 1u;
     for (int r = 0; r < ex->world; ++r) {
-        ex->expected[r] += static_cast<unsigned int>(rows);   // every rank delivers `rows` records per step
-        ep.expected[r] = ex->expected[r];
+        ex->expected[parity][r] += static_cast<unsigned int>(rows);   // every rank delivers `rows` records per step
+        ep.expected[r] = ex->expected[parity][r];
     }
+    ex->steps += 1;
     ep.world = ex->world;
     ep.max_rows = ex->max_rows;
     ep.rows = rows;
@@ -1255,9 +1299,9 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
     const size_t row_bytes = static_cast<size_t>(nh_kv) * 256;
     const size_t stage_bytes = stage ? static_cast<size_t>(B) * s_total_host * nh_kv * 256 : 0;
     ScratchPlan sp = plan_scratch(ctx, rows, nh_q, nh_kv, L.d.hidden, project, qrot, stage_bytes);
-    int rc = ensure_scratch(ctx, sp.total);
+    int rc = ensure_scratch(ctx, sp, st);
     if (rc != DKV_OK) return rc;
-    uint8_t* base = ctx->scratch;
+    uint8_t* base = ctx->scratch.ptr;
     int* cum = reinterpret_cast<int*>(base + sp.cum);
     int* tok_pos = reinterpret_cast<int*>(base + sp.tok_pos);
     int* tok_slot = reinterpret_cast<int*>(base + sp.tok_slot);
@@ -1282,8 +1326,8 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         DKV_CUDA(cudaGetLastError());
         ctx->launches += 1;
     }
-    uint4* stage_k = stage ? reinterpret_cast<uint4*>(base + sp.stage_k) : nullptr;
-    uint4* stage_v = stage ? reinterpret_cast<uint4*>(base + sp.stage_v) : nullptr;
+    uint4* stage_k = stage ? reinterpret_cast<uint4*>(ctx->stage.ptr + sp.stage_k) : nullptr;
+    uint4* stage_v = stage ? reinterpret_cast<uint4*>(ctx->stage.ptr + sp.stage_v) : nullptr;
     if (project) {
         rc = launch_projection(ctx, L, X, static_cast<int>(rows), tok_pos, proj_to_stage ? cum : tok_slot, true, nullptr,
                                reinterpret_cast<float*>(base + sp.splitk), st, false, proj_to_stage ? stage_k : nullptr,
@@ -1380,10 +1424,6 @@ static int run_extend(dkv_context* ctx, const LayerState& L, const void* X, cons
         ep.scale_log2 = scale * 1.4426950408889634f;
         ep.out = static_cast<__nv_bfloat16*>(O);
         ep.status = ctx->status;
-#ifdef DKV_PP_TIMING
-        ep.timing = pp_timing_buffer();
-        ep.dbg_mode = getenv("DKV_PP_MODE") ? atoi(getenv("DKV_PP_MODE")) : 0;
-#endif
         if (ctx->extend_pingpong != 0) {
             // Head slots vary fastest so that the longest (latest) query tiles of ALL heads are dispatched first.
             dim3 grid(nh_kv * nsub, (S_new + 2 * TQ - 1) / (2 * TQ), B);
@@ -1636,11 +1676,11 @@ int dkv_extend_ragged(dkv_context* ctx, int layer_id, const void* X, const void*
 
     const size_t stage_bytes = stage ? static_cast<size_t>(kv_total) * nh_kv * 256 : 0;
     ScratchPlan sp = plan_scratch(ctx, T, nh_q, nh_kv, L.d.hidden, project, false, stage_bytes);
-    rc = ensure_scratch(ctx, sp.total);
+    rc = ensure_scratch(ctx, sp, st);
     if (rc != DKV_OK) return rc;
-    uint8_t* base = ctx->scratch;
-    uint4* ks = stage ? reinterpret_cast<uint4*>(base + sp.stage_k) : nullptr;
-    uint4* vs = stage ? reinterpret_cast<uint4*>(base + sp.stage_v) : nullptr;
+    uint8_t* base = ctx->scratch.ptr;
+    uint4* ks = stage ? reinterpret_cast<uint4*>(ctx->stage.ptr + sp.stage_k) : nullptr;
+    uint4* vs = stage ? reinterpret_cast<uint4*>(ctx->stage.ptr + sp.stage_v) : nullptr;
     // Host pool with projection: the new rows are projected straight into the staging copy, which the attention
     // reads, and go to the host pool from there on the side stream while the attention runs - they cross the host
     // link once, outside the critical path, instead of twice inside it.

@@ -19,6 +19,8 @@ enum StatusBits : unsigned int {
     kStatusBadSlot       = 1u << 1,   // a write-back slot was outside the pool
     kStatusBadPosition   = 1u << 2,   // a RoPE position was outside the cos/sin table
     kStatusTmemTimeout   = 1u << 3,   // the MMA-completion barrier ran out of time
+    kStatusExchangeOrder = 1u << 4,   // sequence-split exchange: a record of another step was found
+    kStatusBadPage       = 1u << 5,   // a page-table index lay outside the table
 };
 
 // Upper bound for any device-side wait, in nanoseconds of %globaltimer.

@@ -47,8 +47,6 @@ struct ExtendParams {
     const int* r_past;
     const int* r_q_row0;
     const int* r_slot0;
-    unsigned long long* timing; // optional cycle counters of the ping-pong kernel (builds with DKV_PP_TIMING), else nullptr
-    int dbg_mode;               // DKV_PP_TIMING builds: 1 = softmax groups skip their arithmetic, 2 = issuers skip the products
 };
 
 // Descriptor of a [64 x 8]-element MN-major, 128-byte-swizzled atom grid: rows (K index) are 128 bytes apart,

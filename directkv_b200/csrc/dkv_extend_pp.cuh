@@ -27,30 +27,6 @@
 
 #include "dkv_extend.cuh"
 
-#ifdef DKV_PP_TIMING
-#define PP_T0(var) const long long var = clock64()
-#define PP_ACC(idx, var) do { pp_acc[idx] += static_cast<unsigned long long>(clock64() - (var)); } while (0)
-#define PP_CNT(idx) do { pp_acc[idx] += 1ull; } while (0)
-#define PP_DECL unsigned long long pp_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define PP_FLUSH do { if (lane == 0 && p.timing) for (int i_ = 0; i_ < 8; ++i_) if (pp_acc[i_]) atomicAdd(p.timing + i_, pp_acc[i_]); } while (0)
-#define PP_MODE(m) ((p.dbg_mode & (m)) != 0)
-#ifdef DKV_PP_TIMING_ISSUER
-#define PP_ACC_S(idx, var)
-#define PP_ACC_I(idx, var) PP_ACC(idx, var)
-#else
-#define PP_ACC_S(idx, var) PP_ACC(idx, var)
-#define PP_ACC_I(idx, var)
-#endif
-#else
-#define PP_MODE(m) false
-#define PP_DECL
-#define PP_FLUSH
-#define PP_T0(var)
-#define PP_ACC(idx, var)
-#define PP_ACC_S(idx, var)
-#define PP_ACC_I(idx, var)
-#define PP_CNT(idx)
-#endif
 
 namespace dkv {
 
@@ -59,10 +35,7 @@ constexpr int kPpThreads = 416;                               // 13 warps: produ
 constexpr int kPpSmem = 2 * kExtTileBytes /*Q0,Q1*/ + kPpSlots * kExtTileBytes + 256 + 1024;
 constexpr float kPpRescaleStep = 8.f;                         // log2 units the maximum may lag behind
 constexpr int kPpHalf = 64;                                   // keys per half-tile
-#ifndef DKV_PP_POLY_MASK
-#define DKV_PP_POLY_MASK 6
-#endif
-constexpr int kPpPolyMask = DKV_PP_POLY_MASK;                 // pairs i with (i & mask) == mask go to the FMA pipe: 6 = every fourth (measured best), 2 = every second, 0x40 = none
+constexpr int kPpPolyMask = 6;                 // pairs i with (i & mask) == mask go to the FMA pipe: 6 = every fourth (measured best), 2 = every second, 0x40 = none
 
 struct PpCtrl {
     uint64_t bar_q;
@@ -85,7 +58,6 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     PpCtrl* ctl = reinterpret_cast<PpCtrl*>(sRing + kPpSlots * kExtTileBytes);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    PP_DECL;
     const int G = p.G, TQ = kExtTile / G;
     const int h = blockIdx.x / p.nsub, sub = blockIdx.x % p.nsub;
     const int qhead0 = h * p.g_total + sub * G;
@@ -114,7 +86,6 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         if (kv_end > s_total) kv_end = s_total;
         n_half[g] = (kv_end + kPpHalf - 1) / kPpHalf;         // n_half[1] >= n_half[0] >= 1 ...
         if (q0 + g * TQ >= s_new) n_half[g] = 0;              // ... unless tile 1 lies past the last new row: it does nothing
-        if (PP_MODE(8) && g == 1) n_half[g] = 0;
     }
     const int n_max = ((n_half[1] > n_half[0] ? n_half[1] : n_half[0]) + 1) >> 1;   // K/V tiles to load
 
@@ -158,13 +129,11 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             }
             for (int q = 0; q < 2 * n_max; ++q) {             // q even: K(q/2), odd: V(q/2)
                 const int s = q % kPpSlots;
-                PP_T0(tp);
                 if (q >= kPpSlots && !mbar_wait_bounded(&ctl->empty[s], ((q / kPpSlots) - 1) & 1)) {
                     atomicOr(p.status, kStatusWaitTimeout);
                     ctl->abort = 1;
                     break;
                 }
-                PP_ACC(5, tp);
                 if (ctl->abort) break;
                 uint8_t* dst = sRing + s * kExtTileBytes;
                 const CUtensorMap* tm = (q & 1) ? &tmV : &tmK;
@@ -191,28 +160,21 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             bool ok = mbar_wait_bounded(&ctl->bar_q, 0);
             for (int t = 0; ok && t < n_g; ++t) {
                 const int q = 2 * (t >> 1), slot = q % kPpSlots;
-                PP_T0(tw);
                 // Buffer t & 1 holds P(t - 2) until the product that reads it is complete (another thread issues it).
                 if (t >= 2) ok = mbar_wait_bounded(&ctl->bar_o[g][t & 1], ((t - 2) >> 1) & 1) && !ctl->abort;
-                PP_ACC(3, tw);
-                PP_T0(t_wr);
                 if (ok && !(t & 1)) ok = mbar_wait_bounded(&ctl->full[slot], (q / kPpSlots) & 1);
-                PP_ACC(4, t_wr);
                 if (!ok) break;
                 tc_fence_after_sync();
-                PP_T0(t_is);
                 const uint64_t kd = k_desc0 + static_cast<uint64_t>((slot * kExtTileBytes + (t & 1) * kPpHalf * 128) >> 4);
                 const uint32_t d = tS + (t & 1) * kPpHalf;
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
-                    if (PP_MODE(2)) break;
                     constexpr int unit = 16;                  // descriptor addresses count 16-byte units
                     const uint64_t off = static_cast<uint64_t>(((k >> 2) * kExtHalfBytes + (k & 3) * 32) / unit);
                     umma_bf16_ss(d, q_desc + off, kd + off, idesc_qk, k > 0 ? 1u : 0u);
                 }
                 umma_commit(&ctl->bar_s[g][t & 1]);
                 if ((t & 1) || t == n_g - 1) umma_commit(&ctl->empty[slot]);   // this tile's last read of K(t >> 1)
-                PP_ACC(6, t_is);
             }
             // K tiles the other query tile still reads: every ring slot expects one arrival per query tile.
             for (int q = 2 * ((n_g + 1) >> 1); ok && q < 2 * n_max; q += 2) {
@@ -244,7 +206,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 const uint32_t pa = tS + (t & 1) * kPpHalf;   // P lies over the S buffer it came from
 #pragma unroll
                 for (int k = 0; k < 4; ++k)                   // 16 keys per step = 8 packed columns of P, 16 rows of V
-                    if (!PP_MODE(2)) umma_bf16_ts(tO, pa + k * 8, vd + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
+                    umma_bf16_ts(tO, pa + k * 8, vd + static_cast<uint64_t>((k * 16 * 128) >> 4), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&ctl->bar_o[g][t & 1]);
                 if ((t & 1) || t == n_g - 1) umma_commit(&ctl->empty[slot]);
             }
@@ -277,23 +239,13 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         for (int t = 0; t < n_g; ++t) {
             const int bf = t & 1;
             // S(t) complete; the product that wrote it was issued after P V(t - 2) had completed and read the buffer.
-            PP_T0(ts);
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_s[g][bf], (t >> 1) & 1) && !ctl->abort);
-            PP_ACC_S(0, ts);
-            PP_CNT(7);
-            PP_T0(tc);
             if (!ok) break;
             tc_fence_after_sync();
             const int col0 = t * kPpHalf;
             const uint32_t tSb = tS + bf * kPpHalf;
             // Warp-uniform: only half-tiles on the diagonal (or holding the end of the request) need the comparison.
             const bool masked = (col0 + kPpHalf - 1 > first_limit) || !(p.scale_log2 > 0.f);
-            if (PP_MODE(1)) {
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&ctl->bar_p[g][bf]);
-                continue;
-            }
             uint32_t r0[32], r1[32];                          // the row's 64 scores stay in registers
             tmem_ld_32x32(tSb, r0);
             tmem_ld_32x32(tSb + 32, r1);
@@ -346,7 +298,6 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 }
             }
             // Probabilities, packed two bf16 per 32-bit column, go back into the first 32 columns of the S buffer.
-            PP_T0(t_ex);
             const float neg_m = -m_used;
             uint32_t pk[32];
             // In place and in phases (scale and shift, exponentials, mask, sums and packing), so that each phase is a
@@ -390,7 +341,6 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             f32x2_split(sa, s4[0], s4[1]);
             f32x2_split(sb, s4[2], s4[3]);
             const float psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-            PP_ACC_S(2, t_ex);
             tmem_st_32x32(tSb, pk);
             tmem_st_wait();
             l += psum;
@@ -412,7 +362,6 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->bar_p[g][bf]);
-            PP_ACC_S(1, tc);
         }
 
         if (n_g == 0) {
@@ -451,7 +400,6 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
         }
     }
 
-    PP_FLUSH;
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 512);

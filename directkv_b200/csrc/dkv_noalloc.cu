@@ -111,14 +111,19 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 
 // Fills a caller-provided descriptor on the host; the pool itself is not touched.
 int encode_pool(CUtensorMap* m, void* base, int64_t n_slots, int nh, int rows) {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            return fail(DKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
-        fn = reinterpret_cast<EncodeTiledFn>(p);
+    static EncodeTiledFn g_encode = nullptr;      // looked up once, under the same lock as the rest of the set-up
+    EncodeTiledFn fn = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_setup_mutex);
+        if (!g_encode) {
+            void* p = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+                q != cudaDriverEntryPointSuccess)
+                return fail(DKV_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+            g_encode = reinterpret_cast<EncodeTiledFn>(p);
+        }
+        fn = g_encode;
     }
     cuuint64_t gdim[3] = {128, (cuuint64_t)nh, (cuuint64_t)n_slots};
     cuuint64_t gstr[2] = {256, (cuuint64_t)nh * 256};
@@ -130,13 +135,18 @@ int encode_pool(CUtensorMap* m, void* base, int64_t n_slots, int nh, int rows) {
     return DKV_OK;
 }
 
-int device_address(void* p, void** out, const char* what) {
+// Address under which the current device reaches `p`: device memory of THIS device, or page-locked host memory.
+// Memory of another GPU is refused: the kernels would read it over NVLink, or fault where there is no peer access.
+int device_address(const void* p, int dev, bool allow_host, void** out, const char* what) {
     cudaPointerAttributes attr;
     NA_CUDA(cudaPointerGetAttributes(&attr, p));
     if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) {
-        *out = p;
+        if (attr.type == cudaMemoryTypeDevice && attr.device != dev)
+            return fail(DKV_ERR_INVALID, "%s lives on device %d but the current device is %d", what, attr.device, dev);
+        *out = const_cast<void*>(p);
         return DKV_OK;
     }
+    if (!allow_host) return fail(DKV_ERR_INVALID, "%s must be device memory of the current device", what);
     if (attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr) {
         *out = attr.devicePointer;
         return DKV_OK;
@@ -157,6 +167,8 @@ extern "C" int dkv_decode_noalloc(const dkv_noalloc_args* a, void* stream) {
     NA_REQUIRE(a->batch > 0 && a->nh_kv > 0 && a->nh_q > 0 && a->nh_q % a->nh_kv == 0,
                "batch, nh_kv, nh_q must be positive and nh_q a multiple of nh_kv");
     NA_REQUIRE(a->n_slots > 0 && a->pt_stride > 0, "n_slots and pt_stride must be positive");
+    NA_REQUIRE(a->n_slots <= static_cast<int64_t>(INT32_MAX), "n_slots (%lld) exceeds the 2^31 - 1 slots a pool can address",
+               (long long)a->n_slots);
     NA_REQUIRE(a->page_size >= 1 && (a->page_size & (a->page_size - 1)) == 0, "page_size (%d) must be a power of two",
                a->page_size);
     NA_REQUIRE(a->q_stride >= static_cast<int64_t>(a->nh_q) * 128 && a->q_stride % 8 == 0 &&
@@ -188,9 +200,12 @@ extern "C" int dkv_decode_noalloc(const dkv_noalloc_args* a, void* stream) {
                     "built-in scratch holds %zu; use dkv_decode (which allocates) for this size",
                     a->batch, a->nh_kv, a->nh_q, need, kScratchBytes - kPartialsOffset);
 
-    void *kd = nullptr, *vd = nullptr;
-    if ((rc = device_address(a->k_pool, &kd, "k_pool")) != DKV_OK) return rc;
-    if ((rc = device_address(a->v_pool, &vd, "v_pool")) != DKV_OK) return rc;
+    void *kd = nullptr, *vd = nullptr, *unused = nullptr;
+    if ((rc = device_address(a->k_pool, dev, true, &kd, "k_pool")) != DKV_OK) return rc;
+    if ((rc = device_address(a->v_pool, dev, true, &vd, "v_pool")) != DKV_OK) return rc;
+    if ((rc = device_address(a->q, dev, false, &unused, "q")) != DKV_OK) return rc;
+    if ((rc = device_address(a->out, dev, false, &unused, "out")) != DKV_OK) return rc;
+    if (a->status_out != nullptr && (rc = device_address(a->status_out, dev, false, &unused, "status_out")) != DKV_OK) return rc;
     const int rows_per_box = a->page_size < kTileTokens ? a->page_size : kTileTokens;
     CUtensorMap tmK, tmV;
     if ((rc = encode_pool(&tmK, kd, a->n_slots, a->nh_kv, rows_per_box)) != DKV_OK) return rc;
@@ -201,9 +216,13 @@ extern "C" int dkv_decode_noalloc(const dkv_noalloc_args* a, void* stream) {
     unsigned int* status = reinterpret_cast<unsigned int*>(base);
     int* cum = reinterpret_cast<int*>(base + kCumOffset);
     float* partials = reinterpret_cast<float*>(base + kPartialsOffset);
-    // The array keeps whatever the previous call left.  The status word must start at zero;
-    // cum_tiles and every partial record that is read are rewritten by this call's own kernels.
-    NA_CUDA(cudaMemsetAsync(status, 0, sizeof(unsigned int), st));
+    // The array keeps whatever the previous call left.  cum_tiles and every partial record that is read are
+    // rewritten by this call's own kernels.  The status word: a caller that passes status_out owns the word the
+    // kernels OR their failure bits into (it clears and reads it when it likes - the way to see a device-side
+    // failure without a synchronising call, e.g. for a call recorded into a graph); otherwise the word inside
+    // the array is used and cleared here, stream-ordered, so that sync_and_check reports this call only.
+    if (a->status_out != nullptr) status = a->status_out;
+    else NA_CUDA(cudaMemsetAsync(status, 0, sizeof(unsigned int), st));
 
     PrepParams prep{};
     prep.seq_lens = a->seq_lens;
@@ -228,6 +247,7 @@ extern "C" int dkv_decode_noalloc(const dkv_noalloc_args* a, void* stream) {
     ap.g_total = g_total;
     ap.nsub = nsub;
     ap.pt_stride = a->pt_stride;
+    ap.pt_rows = a->batch;
     ap.page_size = a->page_size;
     ap.page_shift = 0;
     while ((1 << ap.page_shift) < a->page_size) ++ap.page_shift;
@@ -265,7 +285,9 @@ extern "C" int dkv_decode_noalloc(const dkv_noalloc_args* a, void* stream) {
         unsigned int h = 0;
         NA_CUDA(cudaStreamSynchronize(st));
         NA_CUDA(cudaMemcpy(&h, status, sizeof(h), cudaMemcpyDeviceToHost));
-        if (h != 0) return fail(DKV_ERR_DEVICE_STATUS, "dkv_decode_noalloc: device status 0x%x (a bounded wait ran out)", h);
+        if (h != 0)
+            return fail(DKV_ERR_DEVICE_STATUS, "dkv_decode_noalloc: device status 0x%x (bit 0: a bounded wait ran out; "
+                        "bit 5: a length or row led outside the page table)", h);
     }
     return DKV_OK;
 }

@@ -55,6 +55,7 @@ class _FwdMeta:
     seq_lens_dev: Optional[torch.Tensor] = None       # int32 [bs]
     rows_dev: Optional[torch.Tensor] = None           # int32 [bs] request-pool rows
     req_idx_dev: Optional[torch.Tensor] = None        # int32 [bs] rows of req_to_token
+    graph: bool = False                               # made by a CUDA-graph hook: rows and lengths live in the static tensors
 
 
 class DirectKVBackend(AttentionBackend):
@@ -101,6 +102,7 @@ class DirectKVBackend(AttentionBackend):
         self._token_registered: Dict[int, int] = {}
         self._active_req_ids: set = set()
         self._last_seen: Dict[int, int] = {}
+        self._last_len: Dict[int, int] = {}          # sequence length of each request at its latest step
         self._step_no = 0
         self._start_layer = 0
         # CUDA-graph state: device tensors with stable addresses, refreshed before each replay
@@ -130,7 +132,7 @@ class DirectKVBackend(AttentionBackend):
             self._start_layer = getattr(mr, "start_layer", 0)
             self._pool = self._pool_cls(
                 max_reqs=max_reqs, max_seqlen=max_seqlen, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
-                num_layers=mr.model_config.num_hidden_layers, start_layer=self._start_layer,
+                num_layers=mr.model_config.num_hidden_layers, start_layer=self._start_layer, spare_rows=1,
             )
             logger.info(f"{self._TAG} Pool: {self._pool}")
         for lid in self._wk:
@@ -230,15 +232,17 @@ class DirectKVBackend(AttentionBackend):
             for rid in self._active_req_ids - current:
                 self._pool.free(rid)
                 self._last_seen.pop(rid, None)
+                self._last_len.pop(rid, None)
             self._active_req_ids &= current
         for rid in req_ids:
             if rid not in self._active_req_ids:
-                if not self._pool._free:
+                if self._pool.free_rows == 0:
                     idle = sorted((r for r in self._active_req_ids if r not in current), key=lambda r: self._last_seen.get(r, 0))
                     if idle:
                         self._pool.free(idle[0])
                         self._active_req_ids.discard(idle[0])
                         self._last_seen.pop(idle[0], None)
+                        self._last_len.pop(idle[0], None)
                 self._pool.alloc(rid)
                 self._active_req_ids.add(rid)
             self._last_seen[rid] = self._step_no
@@ -249,10 +253,14 @@ class DirectKVBackend(AttentionBackend):
             return
         if not self._hooks_ready:
             self._setup_hooks()
-        seq_lens_cpu = forward_batch.seq_lens.cpu().tolist()
+        # SGLang keeps a host copy of the lengths; use it and save one device-to-host synchronisation per step.
+        sl_host = getattr(forward_batch, "seq_lens_cpu", None)
+        seq_lens_cpu = sl_host.tolist() if sl_host is not None else forward_batch.seq_lens.cpu().tolist()
         req_ids_cpu = forward_batch.req_pool_indices.cpu().tolist()
         self._ensure_pool()
         self._sync_rows(req_ids_cpu, free_absent=forward_batch.forward_mode.is_decode())
+        for rid, n in zip(req_ids_cpu, seq_lens_cpu):
+            self._last_len[rid] = int(n)
         self._fwd_meta = _FwdMeta(
             seq_lens_cpu=seq_lens_cpu,
             req_pool_indices_cpu=req_ids_cpu,
@@ -275,22 +283,52 @@ class DirectKVBackend(AttentionBackend):
         get_context(self._device_index()).reserve(max_bs, self.num_q_heads, self.num_kv_heads, self.hidden_size)
         logger.info(f"{self._TAG} CUDA graph state: max_bs={max_bs}, layers={len(self._wk)}.")
 
-    def _graph_meta(self, bs: int, req_pool_indices, seq_lens_cpu: List[int]) -> None:
+    def _count_real(self, rid_list: List[int], seq_lens_cpu: List[int]) -> int:
+        """Entries of a replayed batch that are requests.  SGLang pads a replay up to the captured batch size:
+        the padded tail has the fill length and request indices that are stale or zero, so such an index may
+        belong to a live request.  A tail entry counts as padding when its length is the fill value and its
+        index repeats an earlier entry, holds no row, or belongs to a request whose previous length was not
+        fill - 1 (a request that really has the fill length was one token shorter a step ago)."""
+        fill = self.get_cuda_graph_seq_len_fill_value()
+        n = len(rid_list)
+        while n > 0:
+            rid, length = rid_list[n - 1], int(seq_lens_cpu[n - 1])
+            if length != fill:
+                break
+            if not (rid in rid_list[:n - 1] or rid not in self._active_req_ids or self._last_len.get(rid) != fill - 1):
+                break
+            n -= 1
+        return n
+
+    def _graph_meta(self, bs: int, req_pool_indices, seq_lens_cpu: List[int], n_real: Optional[int] = None) -> None:
+        """Device-side lengths and rows of a captured or replayed batch.  Entries from ``n_real`` on are padding:
+        they get the pool's spare row and length 1, so what the graph stores for them (the in-place write of
+        the "new token") reaches no request's row, and they keep no row of their own."""
         rid_list = req_pool_indices[:bs].cpu().tolist()
         self._ensure_pool()
-        self._sync_rows(rid_list)
-        self._cg_rows[:bs].copy_(self._pool.row_table(rid_list), non_blocking=True)
+        if n_real is None:
+            n_real = self._count_real(rid_list, seq_lens_cpu)
+        real = rid_list[:n_real]
+        if real:                       # a capture (placeholders only) changes no request's row
+            self._sync_rows(real)
+        for rid, n in zip(real, seq_lens_cpu):
+            self._last_len[rid] = int(n)
+        rows = [self._pool.row_of(r) for r in real] + [self._pool.pad_row] * (bs - n_real)
+        self._cg_rows[:bs].copy_(torch.tensor(rows, dtype=torch.int32), non_blocking=False)
+        if n_real < bs:
+            self._cg_seq_lens[n_real:bs].fill_(1)
         self._fwd_meta = _FwdMeta(
-            seq_lens_cpu=seq_lens_cpu, req_pool_indices_cpu=rid_list, extend_seq_lens_cpu=None,
-            extend_prefix_lens_cpu=None, seq_lens_dev=self._cg_seq_lens[:bs], rows_dev=self._cg_rows[:bs],
-            req_idx_dev=req_pool_indices[:bs].to(torch.int32),
+            seq_lens_cpu=list(seq_lens_cpu[:n_real]) + [1] * (bs - n_real), req_pool_indices_cpu=rid_list,
+            extend_seq_lens_cpu=None, extend_prefix_lens_cpu=None, seq_lens_dev=self._cg_seq_lens[:bs],
+            rows_dev=self._cg_rows[:bs], req_idx_dev=req_pool_indices[:bs].to(torch.int32), graph=True,
         )
 
     def init_forward_metadata_capture_cuda_graph(self, bs, num_tokens, req_pool_indices, seq_lens, encoder_lens,
                                                  forward_mode, spec_info) -> None:
+        # The batch of a capture is made of placeholders: all of it goes to the spare row.
         fill = self.get_cuda_graph_seq_len_fill_value()
         self._cg_seq_lens[:bs].fill_(fill)
-        self._graph_meta(bs, req_pool_indices, [fill] * bs)
+        self._graph_meta(bs, req_pool_indices, [fill] * bs, n_real=0)
 
     def init_forward_metadata_replay_cuda_graph(self, bs, req_pool_indices, seq_lens, seq_lens_sum, encoder_lens,
                                                 forward_mode, spec_info, seq_lens_cpu=None) -> None:
@@ -312,7 +350,7 @@ class DirectKVBackend(AttentionBackend):
         if x is None or lid not in self._registered:
             return self._decode_token_pool(q2, k, v, layer, forward_batch)
         x2 = x.reshape(bs, self.hidden_size).contiguous()
-        if self._dma_staging and save_kv_cache and not torch.cuda.is_current_stream_capturing():
+        if self._dma_staging and save_kv_cache and not meta.graph and not torch.cuda.is_current_stream_capturing():
             # Eager step over the host-pinned request pool: the copy engines bring the past rows to HBM at the
             # full rate of the host link and the kernels attend that copy (directkv_b200/staging.py).
             if self._stager is None:

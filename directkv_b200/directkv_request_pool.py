@@ -46,7 +46,12 @@ class DirectKVRequestPool:
         start_layer: int = 0,
         dtype: torch.dtype = torch.bfloat16,
         zero_on_alloc: bool = True,
+        spare_rows: int = 0,
     ):
+        # spare_rows: rows behind the max_reqs allocatable ones that never enter the free-list.  The backend
+        # keeps one as the target of the padded entries of a CUDA-graph replay (``pad_row``), whose stores
+        # would otherwise land in some live request's row.
+        self.spare_rows = int(spare_rows)
         self.max_reqs = max_reqs
         self.max_seqlen_pad = _pad64(max_seqlen)
         self.num_kv_heads = num_kv_heads
@@ -56,7 +61,7 @@ class DirectKVRequestPool:
         self.dtype = dtype
         self.zero_on_alloc = zero_on_alloc
 
-        full = (num_layers, max_reqs, self.max_seqlen_pad, num_kv_heads, head_dim)
+        full = (num_layers, max_reqs + self.spare_rows, self.max_seqlen_pad, num_kv_heads, head_dim)
         gib = 2 * torch.Size(full).numel() * dtype.itemsize / 2**30
         logger.info("[DirectKVPool] %d rows x %d layers x K,V [%d, %d, %d] page-locked: %.2f GiB",
                     max_reqs, num_layers, self.max_seqlen_pad, num_kv_heads, head_dim, gib)
@@ -91,6 +96,18 @@ class DirectKVRequestPool:
         row = self._req_to_row.pop(req_id, None)
         if row is not None:
             self._free.append(row)
+
+    @property
+    def free_rows(self) -> int:
+        """Rows that ``alloc`` can still hand out."""
+        return len(self._free)
+
+    @property
+    def pad_row(self) -> int:
+        """First spare row (see ``spare_rows``); ValueError when the pool was built without one."""
+        if self.spare_rows < 1:
+            raise ValueError("the pool was built without spare rows")
+        return self.max_reqs
 
     def row_of(self, req_id: int) -> int:
         """KeyError for an id that holds no row."""

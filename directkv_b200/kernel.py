@@ -181,6 +181,7 @@ def decode(
         lse_out=_ptr(lse_out), partial_out=_ptr(partial_out), pos_offset=_ptr(pos_offset),
         kv_source_layer=int(kv_source_layer), src_page_table=_ptr(src_page_table),
         src_pt_stride=0 if src_page_table is None else src_page_table.stride(0), src_row_map=_ptr(src_row_map),
+        pt_rows=0 if page_table is None else page_table.size(0),
     )
     ctx = get_context(q.device.index)
     if exchange is not None:
@@ -308,6 +309,7 @@ def decode_noalloc(
     softmax_scale: float,
     lse_out: Optional[torch.Tensor] = None,
     sync_and_check: bool = False,
+    status_out: Optional[torch.Tensor] = None,   # [1] int32 CUDA of the caller's: failure bits are OR-ed into it
 ) -> torch.Tensor:
     """Attention-only decode that allocates no device memory (``dkv_decode_noalloc``).
 
@@ -330,6 +332,9 @@ def decode_noalloc(
     _chk(seq_lens.is_cuda and seq_lens.dtype == torch.int32 and seq_lens.numel() == b, "seq_lens must be [B] int32 CUDA")
     _chk(page_table.is_cuda and page_table.dtype == torch.int32 and page_table.dim() == 2 and page_table.stride(1) == 1,
          "page_table must be 2D int32 CUDA with unit inner stride")
+    if status_out is not None:
+        _chk(status_out.is_cuda and status_out.dtype == torch.int32 and status_out.numel() >= 1,
+             "status_out must be an int32 CUDA tensor")
     err = C.create_string_buffer(512)
     a = _lib.NoAllocArgs(
         k_pool=_ptr(k_pool), v_pool=_ptr(v_pool), n_slots=k_pool.numel() // (nh_kv * HEAD_DIM), nh_kv=nh_kv,
@@ -337,6 +342,7 @@ def decode_noalloc(
         out_stride=nh_q * HEAD_DIM, seq_lens=_ptr(seq_lens), page_table=_ptr(page_table),
         pt_stride=page_table.stride(0), softmax_scale=float(softmax_scale), lse_out=_ptr(lse_out),
         sync_and_check=1 if sync_and_check else 0, err_buf=C.cast(err, C.c_char_p), err_buf_len=512,
+        status_out=_ptr(status_out),
     )
     with torch.cuda.device(q.device):
         rc = _lib.load().dkv_decode_noalloc(C.byref(a), _stream())

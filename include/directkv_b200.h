@@ -41,6 +41,8 @@ extern "C" {
 #define DKV_STATUS_BAD_SLOT      (1u << 1)
 #define DKV_STATUS_BAD_POSITION  (1u << 2)
 #define DKV_STATUS_TMEM_TIMEOUT  (1u << 3)
+#define DKV_STATUS_EXCHANGE_ORDER (1u << 4)  /* dkv_decode_exchange: a record of another step arrived (calls of the ranks do not line up) */
+#define DKV_STATUS_BAD_PAGE      (1u << 5)  /* a length or row led outside the page table; the entry was not read */
 
 /* How the token decoded in this step enters dkv_decode. */
 #define DKV_NEW_NONE     0   /* every attended token is already in the pool */
@@ -155,6 +157,9 @@ typedef struct {
     const int32_t* src_page_table;
     int            src_pt_stride;
     const int32_t* src_row_map;
+    int            pt_rows;      /* rows of page_table, or 0 when unknown: with it, a row_map entry beyond the table is
+                                    reported (DKV_STATUS_BAD_PAGE) instead of read; page indices are always held
+                                    below pt_stride */
 } dkv_decode_args;
 
 int dkv_decode(dkv_context* ctx, const dkv_decode_args* args, void* stream);
@@ -286,7 +291,10 @@ int dkv_scatter_kv(dkv_context* ctx, void* k_pool, void* v_pool, int64_t n_slots
  *    clears the status word it needs at zero itself).  Calls that overlap on the GPU race:
  *    keep them on one stream or order them with events.
  *  - errors: the message is written to err_buf (when given); dkv_last_error() is not used.
- *  - the device uses the current device (cudaGetDevice) and the given stream.
+ *  - the call runs on the current device (cudaGetDevice) and the given stream; q, out and a pool in device
+ *    memory must belong to that device (a pool on another GPU is rejected), n_slots must be below 2^31.
+ *  - a device-side failure (a bounded wait that ran out, a length that leads outside the page table) is
+ *    reported by sync_and_check, or, without a synchronising call, through status_out.
  */
 typedef struct {
     void*          k_pool;        /* [n_slots, nh_kv, 128] bf16; host-pinned or device */
@@ -308,6 +316,10 @@ typedef struct {
     int            sync_and_check;/* non-zero: wait for the stream and report a device-side failure */
     char*          err_buf;       /* optional buffer for the error text */
     int            err_buf_len;
+    unsigned int*  status_out;    /* optional device word of the caller's (current device): the kernels OR their
+                                     DKV_STATUS_* bits into it instead of the library's own word, which the next
+                                     call would clear - the way to notice a device-side failure of a call that was
+                                     not made with sync_and_check.  The caller zeroes and reads it. */
 } dkv_noalloc_args;
 
 int dkv_decode_noalloc(const dkv_noalloc_args* args, void* stream);

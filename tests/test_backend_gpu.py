@@ -123,18 +123,18 @@ def test_cuda_graph_hooks_keep_per_request_lengths():
     for n, rid in zip(pre, rids):
         ref.extend(0, rid, x[off:off + n], q[off:off + n], 0)
         off += n
-    # ---- capture one decode step of layer 0 ----
+    # ---- capture one decode step of layer 0 for a batch of 4 (one more than there are requests) ----
     be.init_cuda_graph_state(4, 4)
-    bs = 3
+    bs = 4
     x_s = torch.zeros(bs, H, dtype=torch.bfloat16, device=DEV)
     q_s = torch.zeros(bs, NH_Q * D, dtype=torch.bfloat16, device=DEV)
-    rpi = torch.tensor(rids, dtype=torch.int64, device=DEV)
-    sl = torch.full((bs,), be.get_cuda_graph_seq_len_fill_value(), dtype=torch.int64, device=DEV)
-    be.init_forward_metadata_capture_cuda_graph(bs, bs, rpi, sl, None, DECODE, None)
-    fbd = make_batch(DECODE, [64] * bs, rids, DEV)
-    # the warm-up run stores a token at position fill-1 = 63 of every row; put the real rows back afterwards
+    fill = be.get_cuda_graph_seq_len_fill_value()
+    rpi = torch.zeros(bs, dtype=torch.int64, device=DEV)                       # placeholders, as SGLang passes them
+    sl = torch.full((bs,), fill, dtype=torch.int64, device=DEV)
     torch.cuda.synchronize()
-    saved = [(r, be._pool.k_pool[0][be._pool.row_of(r), 63].clone(), be._pool.v_pool[0][be._pool.row_of(r), 63].clone()) for r in rids]
+    before = [(be._pool.k_pool[0][be._pool.row_of(r)].clone(), be._pool.v_pool[0][be._pool.row_of(r)].clone()) for r in rids]
+    be.init_forward_metadata_capture_cuda_graph(bs, bs, rpi, sl, None, DECODE, None)
+    fbd = make_batch(DECODE, [fill] * bs, [0] * bs, DEV)
     s = torch.cuda.Stream()
     s.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(s):
@@ -146,24 +146,57 @@ def test_cuda_graph_hooks_keep_per_request_lengths():
         layer(hidden_states=x_s)
         out_s = be.forward_decode(q_s, None, None, layer.attn, fbd)
     torch.cuda.synchronize()
-    for r, ks, vs in saved:
-        be._pool.k_pool[0][be._pool.row_of(r), 63] = ks
-        be._pool.v_pool[0][be._pool.row_of(r), 63] = vs
-    # ---- two replays with different, ragged lengths ----
+    # warm-up and capture ran on placeholders: they stored to the pool's spare row, no request's row changed
+    for r, (kb, vb) in zip(rids, before):
+        assert torch.equal(be._pool.k_pool[0][be._pool.row_of(r)], kb), f"capture touched the K row of request {r}"
+        assert torch.equal(be._pool.v_pool[0][be._pool.row_of(r)], vb), f"capture touched the V row of request {r}"
+    # A prefill AFTER the capture makes the engine's scratch grow; the graph must keep working on the memory it
+    # recorded (the outgrown allocation is retired, not freed).
+    n_big = 400
+    fb2 = make_batch(EXTEND, [n_big], [7], DEV, extend_lens=[n_big], prefix_lens=[0])
+    be.init_forward_metadata(fb2)
+    xb, qb = _rand((n_big, H), g), _rand((n_big, NH_Q * D), g)
+    layer(hidden_states=xb.to(DEV))
+    ob = be.forward_extend(qb.to(DEV), None, None, layer.attn, fb2)
+    assert_close(ob, ref.extend(0, 7, xb, qb, 0), "prefill after the capture")
+    # ---- replays with ragged lengths: three requests in a batch padded to four.  The padded entry carries the
+    # fill length and a stale request index that collides with live request 1 (80+ tokens): nothing may be
+    # stored into that request's row at position fill - 1. ----
     lens = list(pre)
-    for step in range(2):
+    for step in range(3):
         cur = [n + 1 for n in lens]
         xs, qs = _rand((bs, H), g), _rand((bs, NH_Q * D), g)
         x_s.copy_(xs)
         q_s.copy_(qs)
-        be.init_forward_metadata_replay_cuda_graph(bs, rpi, torch.tensor(cur, dtype=torch.int64, device=DEV), sum(cur),
-                                                   None, DECODE, None)
+        rpi.copy_(torch.tensor(rids + [1], dtype=torch.int64))
+        sl_now = torch.tensor(cur + [fill], dtype=torch.int64, device=DEV)
+        row1 = be._pool.row_of(1)
+        k63 = be._pool.k_pool[0][row1, fill - 1].clone()
+        be.init_forward_metadata_replay_cuda_graph(bs, rpi, sl_now, sum(cur) + fill, None, DECODE, None,
+                                                   seq_lens_cpu=sl_now.cpu())
         graph.replay()
         torch.cuda.synchronize()
+        from directkv_b200._lib import get_context
+        get_context(0).raise_on_status()
+        assert torch.equal(be._pool.k_pool[0][row1, fill - 1], k63), "a padded entry stored into a live request's row"
         for i, rid in enumerate(rids):
             exp = ref.extend(0, rid, xs[i:i + 1], qs[i:i + 1], lens[i])
             assert_close(out_s[i:i + 1], exp, f"replay {step} req {rid}")
         lens = cur
+
+
+def test_padding_detection_of_graph_replays():
+    """Which tail entries of a replayed batch are padding (host logic of the replay hook)."""
+    be, runner, model, ref = _setup(theta=None)
+    be._ensure_pool()
+    be._sync_rows([1, 2, 6])
+    be._last_len.update({1: 90, 2: 63, 6: 10})
+    fill = be.get_cuda_graph_seq_len_fill_value()
+    assert be._count_real([1, 2, 6], [91, 64, 11]) == 3                 # nothing padded
+    assert be._count_real([1, 2, 6, 0], [91, 64, 11, fill]) == 3        # index 0 holds no row
+    assert be._count_real([1, 6, 2, 2], [91, 11, 64, fill]) == 3        # repeats an earlier entry
+    assert be._count_real([6, 2, 1, 1], [11, 64, fill, fill]) == 2      # request 1 was 90 tokens long, not 63
+    assert be._count_real([1, 6, 2], [91, 11, fill]) == 3               # request 2 was 63 long: really 64 now
 
 
 def test_token_pool_path_when_no_hidden_states():

@@ -63,3 +63,4 @@ def test_struct_layouts_match_header_field_order():
 
     assert fields("dkv_layer_desc") == [f[0] for f in _lib.LayerDesc._fields_]
     assert fields("dkv_decode_args") == [f[0] for f in _lib.DecodeArgs._fields_]
+    assert fields("dkv_noalloc_args") == [f[0] for f in _lib.NoAllocArgs._fields_]
