@@ -10,16 +10,22 @@ Workload: the OPT-6.7B layer configuration (hidden 4096, 32 MHA heads, head_dim 
 table; seeded synthetic tensors (there are no model weights or traces on the machine).
 
 Reported on one JSON line:
-  value  - KV GB/s with the KV pool resident in HBM (inputs on the device before timing starts)
-  e2e    - the same metric through the public Python API with the KV pool in page-locked HOST
-           memory: the kernel streams it over PCIe inside the timed region, and every step also
-           copies X, Q and the lengths host->device from pinned memory and the output back.
-  roofline     - the KV-streaming kernel alone: algorithmic KV bytes per launch / its mean launch
-                 duration (CUDA events on the launching stream) against the measured HBM copy peak
+  value  - host-KV GB/s: KV bytes attended per second with the KV pool in page-locked HOST memory,
+           streamed over the host link by the kernel inside the timed region (X, Q and the lengths
+           already on the device)
+  e2e    - the same through the public Python API, with every step also copying X, Q and the
+           lengths host->device from pinned memory and the output back
+  roofline     - the KV-streaming kernel of those steps: algorithmic KV bytes per launch / its mean
+                 launch duration (CUDA events on the launching stream) against the pinned
+                 host->device copy rate measured in the same run with all ranks copying at once
+  hbm          - the same step with the pool resident in HBM, against the measured HBM copy peak
   cpu_baseline - the CPU restatement of the reference's torch path, timed on the host cores
-  clocks, gpu_launches, host_link (pinned host->device copy bandwidth measured in this run)
-With N > 1 (torchrun) every rank owns its own 32-head shard and its own host pool; there is no
-data-path collective (per-GPU work is fixed: weak scaling).
+  clocks, gpu_launches
+With N > 1 (torchrun) the layer's 32 KV heads are partitioned over the ranks (32 / N each, every rank
+its own host pool, no data-path collective: the same total work at every N), and two more objects
+are added: multi_gpu_check (head shard and both forms of the sequence split against the oracle on a
+small case) and seq_split (one 1M-token request split by sequence, merged with NCCL or by the
+fused peer-memory exchange).
 
 --impl reference times the reference's torch attention path, restated for the CPU in fp32
 (oracle/), on the host cores for the same configuration.
@@ -45,7 +51,7 @@ from directkv_b200 import workloads  # noqa: E402
 
 CFG_ID = 1
 PAGE = 16
-METRIC = "decode_attention_kv_gbps"
+METRIC = "decode_attention_host_kv_gbps"
 UNIT = "GB/s"
 
 
@@ -117,39 +123,59 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_reference_time(steps: int, warmup: int, lens, sample_idx):
-    """Times the reference's torch attention path (fp32, CPU) on a bounded sample of the workload."""
+def workload_config(world: int, lens):
+    """The `config` object of the JSON line; both arms (this engine, --impl reference) print the same one."""
+    shape = workloads.OPT_6_7B
+    return {
+        "workload": "opt-6.7b layer decode, 16 ragged requests ctx U[512,8192], 16-token permuted pages",
+        "kv_pool": "page-locked host memory, read over the host link inside the timed region",
+        "kv_bytes_per_step": workloads.kv_bytes(shape, lens), "tokens": int(sum(lens)), "page_size": PAGE,
+        "parallelism": (f"kv-head partition x{world}: {shape.nh_kv // world} of the layer's {shape.nh_kv} KV heads and one "
+                        f"host pool per rank, no data-path collective (total work fixed)"),
+        "l2": "inputs larger than L2 (0.98 GB of KV per step vs 126 MB)",
+    }
+
+
+def cpu_reference_time(steps: int, warmup: int, lens, budget_s: float = 150.0):
+    """Times the reference's torch attention path (fp32, CPU, all host threads) on the whole batch.  `steps` timed
+    passes after `warmup` untimed ones; the loop stops early only when the time budget is spent, and returns how
+    many passes it timed."""
     from oracle import directkv_oracle as orc
 
     torch.set_num_threads(os.cpu_count() or 1)
     shape = workloads.OPT_6_7B
-    sub = [lens[i] for i in sample_idx]
-    case = workloads.make_decode_case(shape, sub, PAGE, CFG_ID, "cpu", kv_on_host=True)
-    args = (case["x"], case["wk"], case["wv"], case["q"], case["k_pool"], case["v_pool"], case["page_table"], sub,
+    case = workloads.make_decode_case(shape, lens, PAGE, CFG_ID, "cpu", kv_on_host=True)
+    args = (case["x"], case["wk"], case["wv"], case["q"], case["k_pool"], case["v_pool"], case["page_table"], lens,
             PAGE, None, shape.scale)
+    t_start = time.perf_counter()
     for _ in range(warmup):
         orc.decode_layer(*args)
-    t0 = time.perf_counter()
-    for _ in range(steps):
+    done, t0 = 0, time.perf_counter()
+    while done < steps:
         orc.decode_layer(*args)
-    dt = (time.perf_counter() - t0) / steps
-    nbytes = workloads.kv_bytes(shape, sub)
-    return nbytes / dt / 1e9, dt * 1e3, torch.get_num_threads(), f"{len(sub)} of {len(lens)} requests ({sum(sub)} tokens) per step"
+        done += 1
+        if time.perf_counter() - t_start > budget_s:
+            break
+    dt = (time.perf_counter() - t0) / done
+    nbytes = workloads.kv_bytes(shape, lens)
+    sample = f"all {len(lens)} requests ({sum(lens)} tokens) per step, {done} steps after {warmup} warm-ups"
+    return nbytes / dt / 1e9, dt * 1e3, torch.get_num_threads(), sample, done
 
 
-def run_reference(args, rank):
+def run_reference(args, rank, world):
+    """--impl reference: the reference's own implementation of the path that runs here - its torch attention path
+    (gather by slot + scaled_dot_product_attention; the kernel is sm_90a-only), restated in fp32 for the CPU - on
+    the whole batch, all host threads, with the --steps / --warmup given.  Under torchrun rank 0 alone runs."""
     if rank != 0:
         return
     lens = c2_lengths()
-    steps = max(1, min(args.steps, 10))
-    gbs, ms, cores, sample = cpu_reference_time(steps, max(1, min(args.warmup, 2)), lens, list(range(0, 16, 4)))
+    gbs, ms, cores, sample, done = cpu_reference_time(args.steps, args.warmup, lens)
     line = {
-        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "opt-6.7b layer decode, 16 ragged requests ctx U[512,8192], 16-token permuted pages",
-                   "note": "reference's torch attention path (gather by slot + scaled_dot_product_attention) "
-                           "restated in fp32 on the CPU; the reference's own kernel is sm_90a-only"},
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus, "steps": done,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(world, lens),
+        "note": "reference's torch attention path (gather by slot + scaled_dot_product_attention) restated in fp32 "
+                "on the CPU; the reference's own kernel is sm_90a-only",
         "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -221,19 +247,35 @@ def _graphed(fn, n=1):
     return g.replay
 
 
-def _oracle_error(case, shape, lens, page, out, pick):
-    """max |err| and max relative err of request `pick` against the CPU oracle (checker only)."""
+def _oracle_picks(lens, seed=0):
+    """Requests a full-size run is checked on: the longest, the shortest and two seeded random ones."""
+    order = sorted(range(len(lens)), key=lambda i: lens[i])
+    picks = [order[-1], order[0]]
+    g = torch.Generator().manual_seed(977 + seed)
+    for i in torch.randperm(len(lens), generator=g).tolist():
+        if i not in picks and len(picks) < min(4, len(lens)):
+            picks.append(i)
+    return picks
+
+
+def _oracle_error(case, shape, lens, page, out, picks):
+    """max |err| and max relative err of the requests `picks` against the CPU oracle (checker only, outside every
+    timed region)."""
     from oracle import directkv_oracle as orc
 
-    sub = [pick]
-    ref = orc.decode_layer(case["x"][sub].cpu(), case["wk"].cpu(), case["wv"].cpu(), case["q"][sub].cpu(),
-                           case["k_pool"].cpu() if case["k_pool"].is_cuda else case["k_pool"],
-                           case["v_pool"].cpu() if case["v_pool"].is_cuda else case["v_pool"],
-                           case["page_table"][sub].cpu(), [lens[pick]], page,
-                           None if case["cos_sin"] is None else case["cos_sin"].cpu(), shape.scale, save_kv_cache=False)
-    got = out[pick].float().cpu().view_as(ref[0])
-    err = (got - ref[0]).abs()
-    return float(err.max()), float((err / ref[0].abs().clamp_min(1e-2)).max())
+    k_cpu = case["k_pool"].cpu() if case["k_pool"].is_cuda else case["k_pool"]
+    v_cpu = case["v_pool"].cpu() if case["v_pool"].is_cuda else case["v_pool"]
+    worst_abs, worst_rel = 0.0, 0.0
+    for pick in picks:
+        sub = [pick]
+        ref = orc.decode_layer(case["x"][sub].cpu(), case["wk"].cpu(), case["wv"].cpu(), case["q"][sub].cpu(), k_cpu, v_cpu,
+                               case["page_table"][sub].cpu(), [lens[pick]], page,
+                               None if case["cos_sin"] is None else case["cos_sin"].cpu(), shape.scale, save_kv_cache=False)
+        got = out[pick].float().cpu().view_as(ref[0])
+        err = (got - ref[0]).abs()
+        worst_abs = max(worst_abs, float(err.max()))
+        worst_rel = max(worst_rel, float((err / ref[0].abs().clamp_min(1e-2)).max()))
+    return worst_abs, worst_rel
 
 
 def measure_extend(dev, steps, warmup):
@@ -360,7 +402,7 @@ def run_sweep(args, rank, world, local_rank, dev, dist):
             fn()
             sync()
             ctx.raise_on_status()
-            err = _oracle_error(case, sh, lens, PAGE, out, min(range(len(lens)), key=lambda i: lens[i])) if rank == 0 else None
+            err = _oracle_error(case, sh, lens, PAGE, out, _oracle_picks(lens, cfg)) if rank == 0 else None
             replay = _graphed(fn) if layers == 1 else fn
             n_it = iters if mode == "hbm" else max(5, min(iters, int(2000 / max(1.0, workloads.kv_bytes(sh, lens) * layers / 50e6))))
             med, best = _median_ms(replay, n_it, 3 if mode == "host" else 20, sync)
@@ -467,10 +509,171 @@ def run_sweep(args, rank, world, local_rank, dev, dist):
             write_longctx_csv(args.longctx_csv, longctx_rows)
 
 
+# ---------------------------------------------------------------------------------------------------
+# Multi-GPU parts of the default run: parity on a small case, and the 1M-token sequence split.
+# ---------------------------------------------------------------------------------------------------
+def multi_gpu_check(rank, world, dev, dist):
+    """Head shard, sequence split with the NCCL all-gather and with the fused peer-memory exchange, each against the
+    CPU oracle on a small seeded case (the case of tests/test_sharding_gpu.py; outside every timed region).
+    Returns the worst absolute errors; raises when one misses the parity bar or the device status word is set."""
+    from directkv_b200 import kernel, sharding
+    from directkv_b200._lib import get_context
+    from oracle import directkv_oracle as orc
+
+    ctx = get_context(dev.index)
+    atol, rtol = 2e-2, 1e-2
+
+    def worst(out, ref, what):
+        err = (out.float().cpu() - ref).abs()
+        if not bool((err <= atol + rtol * ref.abs()).all()):
+            raise RuntimeError(f"multi_gpu_check: {what} outside the parity bar on rank {rank}: max abs err {float(err.max()):.3e}")
+        return float(err.max())
+
+    def allmax(x):
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    shape = workloads.LayerShape("check", 256, 8 * world, 2 * world, 10000.0)     # 2 KV heads per rank
+    lens = [5, 130, 1000, 64]
+    full = workloads.make_decode_case(shape, lens, PAGE, 11, "cpu", kv_on_host=True)
+    ref = orc.decode_layer(full["x"], full["wk"], full["wv"], full["q"], full["k_pool"].clone(), full["v_pool"].clone(),
+                           full["page_table"], lens, PAGE, full["cos_sin"], shape.scale)
+    sh = sharding.HeadShard(rank, world, shape.nh_q, shape.nh_kv)
+    wk, wv = sh.weights(full["wk"], full["wv"])
+    k_loc, v_loc = sh.pool(full["k_pool"]).pin_memory(), sh.pool(full["v_pool"]).pin_memory()
+    kernel.register_layer(40, k_loc, v_loc, wk.to(dev), wv.to(dev), full["cos_sin"].to(dev), page_size=PAGE, device=dev.index)
+    out = kernel.decode(40, sh.queries(full["q"]).to(dev), full["seq_lens"].to(dev), shape.scale,
+                        page_table=full["page_table"].to(dev), x=full["x"].to(dev))
+    ctx.raise_on_status()
+    e_head = worst(out, ref[:, sh.q_heads.start:sh.q_heads.stop], "head-sharded output")
+    kernel.unregister_layer(40)
+
+    one_shape = workloads.LayerShape("check1", 256, 8, 2, 10000.0)
+    n = 3000
+    one = workloads.make_decode_case(one_shape, [n + 1], PAGE, 12, "cpu", kv_on_host=True)
+    plan = sharding.plan_sequence_split(n + 1, world, PAGE)
+    owner = sharding.owner_of_new_token(plan)
+    s0, e0 = plan[rank]
+    pages = one["page_table"][:, s0 // PAGE: -(-e0 // PAGE)].contiguous().to(dev)
+    if pages.size(1) == 0:
+        pages = torch.zeros(1, 1, dtype=torch.int32, device=dev)
+    kp, vp = one["k_pool"].pin_memory(), one["v_pool"].pin_memory()
+    kernel.register_layer(41, kp, vp, one["wk"].to(dev), one["wv"].to(dev), one["cos_sin"].to(dev), page_size=PAGE, device=dev.index)
+    is_owner = rank == owner
+    lens_dev = torch.tensor([e0 - s0], dtype=torch.int32, device=dev)
+    off_dev = torch.tensor([s0], dtype=torch.int32, device=dev)
+    x_dev = one["x"].to(dev) if is_owner else None
+    ref1 = orc.decode_layer(one["x"], one["wk"], one["wv"], one["q"], one["k_pool"].clone(), one["v_pool"].clone(),
+                            one["page_table"], [n + 1], PAGE, one["cos_sin"], one_shape.scale)
+    o = sharding.sequence_split_decode(41, one["q"].to(dev), lens_dev, one_shape.scale, pages, x=x_dev,
+                                       pos_offset=off_dev if is_owner else None)
+    ctx.raise_on_status()
+    e_nccl = worst(o, ref1, "sequence split (NCCL) output")
+    # Fused exchange: steps back to back without host synchronisation, a different query in each.
+    steps = 200
+    g = torch.Generator().manual_seed(77)
+    q_steps = torch.randn(steps, 1, one_shape.nh_q, 128, generator=g).to(torch.bfloat16)
+    q_dev = q_steps.to(dev)
+    outs = torch.empty(steps, 1, one_shape.nh_q, 128, dtype=torch.bfloat16, device=dev)
+    ex = sharding.PartialExchange(max_rows=64, device=dev.index)
+    for it in range(steps):
+        kernel.decode(41, q_dev[it], lens_dev, one_shape.scale, page_table=pages, x=x_dev,
+                      pos_offset=off_dev if is_owner else None, out=outs[it], exchange=ex.handle)
+    torch.cuda.synchronize()
+    ctx.raise_on_status()
+    e_fused = 0.0
+    k_ref, v_ref = one["k_pool"].clone(), one["v_pool"].clone()
+    for it in range(steps):
+        r_it = orc.decode_layer(one["x"], one["wk"], one["wv"], q_steps[it], k_ref, v_ref, one["page_table"], [n + 1], PAGE,
+                                one["cos_sin"], one_shape.scale)
+        e_fused = max(e_fused, worst(outs[it], r_it, f"sequence split (fused exchange) output of step {it}"))
+    ex.close()
+    kernel.unregister_layer(41)
+    return {"head_shard_max_err": allmax(e_head), "seq_split_nccl_max_err": allmax(e_nccl),
+            "seq_split_fused_max_err": allmax(e_fused), "steps": steps, "bar": "2e-2 abs + 1e-2 rel", "status": 0}
+
+
+def measure_seq_split(rank, world, dev, dist, ctx_len=1 << 20, layers=8, iters=3):
+    """One Llama-3-8B request of `ctx_len` tokens split by sequence over the ranks, pool in pinned host memory:
+    `layers` layer steps per timed call (one layer's pool is used for all of them), partial (O, m, l) merged with
+    an NCCL all-gather or by the fused peer-memory exchange.  Device-timed, maximum over ranks."""
+    from directkv_b200 import kernel, sharding
+    from directkv_b200._lib import get_context
+
+    ctx = get_context(dev.index)
+    shape = workloads.LLAMA3_8B
+    plan = sharding.plan_sequence_split(ctx_len + 1, world, PAGE)
+    owner = sharding.owner_of_new_token(plan)
+    s0, e0 = plan[rank]
+    n_loc = e0 - s0
+    case = workloads.make_decode_case(shape, [max(n_loc, 1)], PAGE, 2 + rank, dev, kv_on_host=True)
+    cs = workloads.build_cos_sin(ctx_len + 2, shape.rope_theta, device=dev)
+    kernel.register_layer(42, case["k_pool"], case["v_pool"], case["wk"], case["wv"], cs, page_size=PAGE, device=dev.index)
+    lens_dev = torch.tensor([n_loc], dtype=torch.int32, device=dev)
+    off = torch.tensor([s0], dtype=torch.int32, device=dev)
+    is_owner = rank == owner
+    # every rank attends the same query (rank 0's)
+    q = case["q"].clone()
+    dist.broadcast(q, src=0)
+    x = case["x"] if is_owner else None
+    ex = sharding.PartialExchange(max_rows=shape.nh_q, device=dev.index)
+    out_f = torch.empty_like(q)
+
+    def run_nccl():
+        o = None
+        for _ in range(layers):
+            o = sharding.sequence_split_decode(42, q, lens_dev, shape.scale, case["page_table"], x=x,
+                                               pos_offset=off if is_owner else None)
+        return o
+
+    def run_fused():
+        for _ in range(layers):
+            kernel.decode(42, q, lens_dev, shape.scale, page_table=case["page_table"], x=x,
+                          pos_offset=off if is_owner else None, out=out_f, exchange=ex.handle)
+        return out_f
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            dist.barrier(device_ids=[dev.index])
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ts.append(float(t.item()))
+        return statistics.median(ts)
+
+    ms_nccl = timed(run_nccl)
+    o_nccl = run_nccl().float().clone()
+    ms_fused = timed(run_fused)
+    o_fused = run_fused().float().view_as(o_nccl)
+    torch.cuda.synchronize()
+    ctx.raise_on_status()
+    diff = torch.tensor([float((o_nccl - o_fused).abs().max())], dtype=torch.float64, device=dev)
+    dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+    ex.close()
+    kernel.unregister_layer(42)
+    kvb = workloads.kv_bytes(shape, [ctx_len + 1]) * layers
+    best = min(ms_nccl, ms_fused)
+    return {"workload": "llama3-8b layer, one request, KV in pinned host memory, split by sequence over the ranks",
+            "ctx": ctx_len, "layers": layers, "ms_per_layer_nccl": ms_nccl / layers, "ms_per_layer_fused": ms_fused / layers,
+            "kv_gbs_aggregate": kvb / best / 1e6, "kv_gbs_aggregate_nccl": kvb / ms_nccl / 1e6,
+            "kv_gbs_aggregate_fused": kvb / ms_fused / 1e6, "nccl_vs_fused_max_diff": float(diff.item()),
+            "note": "one layer's pool re-used for all layers of a call; time = maximum over ranks, median of "
+                    f"{iters} calls of {layers} layers"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--variant", type=int, default=None, help="override the streaming-kernel variant")
@@ -481,6 +684,7 @@ def main():
     ap.add_argument("--sweep-out", default="sweep.jsonl")
     ap.add_argument("--longctx-csv", default=None,
                     help="with --sweep C3: also append rows in the column layout of the reference's long-context benchmark")
+    ap.add_argument("--seq-split-ctx", type=int, default=1 << 20, help="context of the sequence-split arm (N > 1)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -489,7 +693,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
-        run_reference(args, rank)
+        run_reference(args, rank, world)
         return
 
     import torch.distributed as dist
@@ -513,31 +717,43 @@ def main():
         if world > 1:
             dist.barrier(device_ids=[local_rank])
 
-    def sum_over_ranks(x: float) -> float:
+    def reduce_ranks(x: float, op) -> float:
         if world == 1:
             return x
         t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        dist.all_reduce(t, op=op)
         return float(t.item())
 
-    def max_over_ranks(x: float) -> float:
+    def sum_over_ranks(x):
+        return reduce_ranks(x, dist.ReduceOp.SUM)
+
+    def max_over_ranks(x):
+        return reduce_ranks(x, dist.ReduceOp.MAX)
+
+    def per_rank(x: float):
+        """min / mean / max of one figure over the ranks."""
         if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+            return {"min": x, "mean": x, "max": x}
+        t = torch.zeros(world, dtype=torch.float64, device=dev)
+        t[rank] = x
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        v = t.tolist()
+        return {"min": min(v), "mean": sum(v) / len(v), "max": max(v)}
 
     if args.only == "extend":
         run_extend_probe(args, dev)
         return
 
-    shape = workloads.OPT_6_7B
+    full = workloads.OPT_6_7B
+    if full.nh_kv % world != 0:
+        raise SystemExit(f"--gpus {world}: the layer's {full.nh_kv} KV heads do not divide over {world} ranks")
+    shape = full.shard(world) if world > 1 else full        # this rank's KV heads and their query heads
     lens = c2_lengths()
     ctx = get_context(local_rank)
     if args.variant is not None:
         ctx.set("attn_variant", args.variant)
 
-    # ---- inputs: one host-resident pool, one HBM-resident copy of it --------------------------------
+    # ---- inputs: this rank's host-resident pool, and an HBM-resident copy of it ---------------------
     case = workloads.make_decode_case(shape, lens, PAGE, CFG_ID + 100 * rank, dev, kv_on_host=True)
     k_host, v_host = case["k_pool"], case["v_pool"]
     k_hbm, v_hbm = k_host.to(dev), v_host.to(dev)
@@ -550,9 +766,12 @@ def main():
     out_dev = torch.empty_like(case["q"])
     out_pin = torch.empty(out_dev.shape, dtype=out_dev.dtype, pin_memory=True)
     table = case["page_table"]
-    kv_total = workloads.kv_bytes(shape, lens)                       # every attended token, incl. the new one
-    kv_streamed = workloads.kv_bytes(shape, [n - 1 for n in lens])   # what the streaming kernel reads
+    kv_total = workloads.kv_bytes(shape, lens)                       # this rank: every attended token, incl. the new one
+    kv_streamed = workloads.kv_bytes(shape, [n - 1 for n in lens])   # this rank: what the streaming kernel reads
     kv_all_ranks = sum_over_ranks(float(kv_total))
+
+    def step_host():
+        kernel.decode(0, case["q"], case["seq_lens"], shape.scale, page_table=table, x=case["x"], out=out_dev)
 
     def step_hbm():
         kernel.decode(1, case["q"], case["seq_lens"], shape.scale, page_table=table, x=case["x"], out=out_dev)
@@ -565,6 +784,7 @@ def main():
         out_pin.copy_(out_dev, non_blocking=True)
 
     def timed(fn, steps, warmup):
+        """ms per step of `steps` calls after `warmup` untimed ones: (maximum over ranks, this rank's own)."""
         for _ in range(warmup):
             fn()
         torch.cuda.synchronize()
@@ -577,117 +797,182 @@ def main():
         e1.record()
         torch.cuda.synchronize()
         barrier()
-        return max_over_ranks(e0.elapsed_time(e1)) / steps
+        own = e0.elapsed_time(e1) / steps
+        return max_over_ranks(own), own
+
+    def link_rate(n_copies=6):
+        """Pinned host->device cudaMemcpyAsync of 1 GiB, GB/s: the median of the middle copies of a back-to-back run
+        (with several ranks the first and last copy may run while other ranks are still idle)."""
+        nb = 1 << 30
+        hbuf = torch.empty(nb, dtype=torch.uint8, pin_memory=True)
+        dbuf = torch.empty(nb, dtype=torch.uint8, device=dev)
+        dbuf.copy_(hbuf, non_blocking=True)
+        torch.cuda.synchronize()
+        barrier()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_copies + 1)]
+        evs[0].record()
+        for i in range(n_copies):
+            dbuf.copy_(hbuf, non_blocking=True)
+            evs[i + 1].record()
+        torch.cuda.synchronize()
+        ts = [evs[i].elapsed_time(evs[i + 1]) for i in range(n_copies)]
+        barrier()
+        del hbuf, dbuf
+        mid = ts[1:-1] if world > 1 else ts
+        return nb / statistics.median(mid) / 1e6, nb / min(ts) / 1e6
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
 
+    # ---- host link: every rank copying at once, behind a barrier -----------------------------------------
+    link_gbs, link_best = link_rate()
+    link_ranks = per_rank(link_gbs)
+
+    # ---- host-KV mode: `value` -------------------------------------------------------------------------------
+    # X, Q and the lengths are on the device; the KV pool is page-locked host memory that the streaming kernel reads
+    # over the host link inside the timed region.  Every launch of that kernel is bracketed by CUDA events on the
+    # launching stream (the roofline figure comes from the same timed steps).
+    for _ in range(args.warmup):
+        step_host()
+    ctx.profile_read(reset=True)
+    ctx.set("profile_attn", 1)
+    ms_host, ms_host_own = timed(step_host, args.steps, 0)
+    attn_ms, attn_n, launches_host = ctx.profile_read(reset=True)
+    ctx.set("profile_attn", 0)
+    ctx.raise_on_status()
+    attn_avg_ms = attn_ms / max(attn_n, 1)
+    host_rank_gbs = per_rank(kv_total / ms_host_own / 1e6)
+    attn_rank_gbs = per_rank(kv_streamed / attn_avg_ms / 1e6 if attn_avg_ms > 0 else 0.0)
+
     if args.only == "host":
-        ms = timed(step_e2e, max(1, min(args.steps, 20)), args.warmup)
-        ctx.raise_on_status()
         if rank == 0:
             sampler.stop()
-            print(json.dumps({"metric": METRIC, "value": kv_all_ranks / ms / 1e6, "unit": UNIT, "ms_per_step": ms,
-                              "partial": "host-KV mode only"}))
+            print(json.dumps({"metric": METRIC, "value": kv_all_ranks / ms_host / 1e6, "unit": UNIT, "ms_per_step": ms_host,
+                              "attn_avg_ms": attn_avg_ms, "partial": "host-KV mode only"}))
         if world > 1:
             dist.destroy_process_group()
         return
 
-    # ---- HBM-resident mode ---------------------------------------------------------------------------------
-    # (a) roofline of the streaming kernel: K eager steps with every launch of it bracketed by CUDA events on
-    #     the launching stream; (b) `value`: K steps replayed from a CUDA graph of the per-layer launch sequence
-    #     (what a serving loop does; it also keeps the host out of the timed region when 8 ranks share a CPU).
+    # ---- the same through the public API with per-step host copies: `e2e` -----------------------------------
+    ms_e2e, _ = timed(step_e2e, args.steps, 3)
+    ctx.raise_on_status()
+
+    # ---- HBM-resident mode (secondary object) ------------------------------------------------------------------
+    # (a) roofline of the streaming kernel: eager steps with every launch of it bracketed by CUDA events; (b) the
+    #     step time: K steps captured in one CUDA graph (a model runs its layers that way), the graph replayed R
+    #     times so that the timed work exceeds 0.2 s; median and spread over the R replays.
     for _ in range(args.warmup):
         step_hbm()
     ctx.profile_read(reset=True)
     ctx.set("profile_attn", 1)
-    ms_hbm_eager = timed(step_hbm, args.steps, 0)
-    attn_ms, attn_n, launches_hbm = ctx.profile_read(reset=True)
+    ms_hbm_eager, _ = timed(step_hbm, args.steps, 0)
+    hattn_ms, hattn_n, _ = ctx.profile_read(reset=True)
     ctx.set("profile_attn", 0)
     ctx.raise_on_status()
-    # A model runs its layers from one CUDA graph, so the K timed steps are K layer passes captured in one graph
-    # and launched once; the same steps as one graph launch each are reported beside it.
-    replay_one = _graphed(step_hbm)
-    ms_hbm_one = timed(replay_one, args.steps, args.warmup)
     replay_hbm = _graphed(step_hbm, args.steps)
-    replay_hbm()
-    ms_hbm = timed(replay_hbm, 1, 0) / args.steps
+    for _ in range(3):
+        replay_hbm()
+    torch.cuda.synchronize()
+    est = max(ms_hbm_eager * args.steps, 1e-3)
+    n_rep = int(min(400, max(10, 250.0 / est)))
+    barrier()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(n_rep + 1)]
+    evs[0].record()
+    for i in range(n_rep):
+        replay_hbm()
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    barrier()
+    reps = sorted(evs[i].elapsed_time(evs[i + 1]) / args.steps for i in range(n_rep))
+    ms_hbm_own = statistics.median(reps)
+    ms_hbm = max_over_ranks(ms_hbm_own)
+    hbm_total_s = max_over_ranks(evs[0].elapsed_time(evs[n_rep]) / 1e3)
     ctx.raise_on_status()
+    hattn_avg_ms = hattn_ms / max(hattn_n, 1)
 
     if args.only == "hbm":
         if rank == 0:
             sampler.stop()
-            print(json.dumps({"metric": METRIC, "value": kv_all_ranks / ms_hbm / 1e6, "unit": UNIT,
-                              "ms_per_step": ms_hbm, "attn_avg_ms": attn_ms / max(attn_n, 1), "partial": "hbm only"}))
+            print(json.dumps({"metric": "decode_attention_hbm_kv_gbps", "value": kv_all_ranks / ms_hbm / 1e6, "unit": UNIT,
+                              "ms_per_step": ms_hbm, "attn_avg_ms": hattn_avg_ms, "partial": "hbm only"}))
         if world > 1:
             dist.destroy_process_group()
         return
 
-    # ---- host-KV mode through the public API: `e2e` -----------------------------------------------------
-    e2e_steps = max(3, min(args.steps, 20))
-    ms_e2e = timed(step_e2e, e2e_steps, 3)
-    ctx.raise_on_status()
-
-    # ---- host link peak: pinned host->device copy of >= 1 GiB --------------------------------------
-    nb = 1 << 30
-    hbuf = torch.empty(nb, dtype=torch.uint8, pin_memory=True)
-    dbuf = torch.empty(nb, dtype=torch.uint8, device=dev)
-    best = 1e30
-    for _ in range(5):
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        dbuf.copy_(hbuf, non_blocking=True)
-        b.record()
-        torch.cuda.synchronize()
-        best = min(best, a.elapsed_time(b))
-    link_gbs = nb / best / 1e6
-    del hbuf, dbuf
-
     clocks = sampler.stop() if rank == 0 else None
+
+    # ---- N > 1: parity of the partitionings, and the sequence split at 1M tokens (outside the timed regions above) ----
+    mg_check = seq_split = None
+    if world > 1:
+        kernel.unregister_layer(0)
+        kernel.unregister_layer(1)
+        del k_hbm, v_hbm, k_host, v_host, case
+        torch.cuda.empty_cache()
+        mg_check = multi_gpu_check(rank, world, dev, dist)
+        seq_split = measure_seq_split(rank, world, dev, dist, ctx_len=args.seq_split_ctx)
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
     peak, peak_kind = measured_peaks()
-    attn_avg_ms = attn_ms / max(attn_n, 1)
-    achieved = kv_streamed / attn_avg_ms / 1e6 if attn_avg_ms > 0 else 0.0
-    cpu_gbs, cpu_ms, cores, sample = cpu_reference_time(2, 1, lens, [0, 8]) if world == 1 else (None, None, None, None)
-    # Secondary number, outside the timed region of the headline: the chunked-prefill path on this GPU.
+    achieved_host = kv_streamed / attn_avg_ms / 1e6 if attn_avg_ms > 0 else 0.0
+    achieved_hbm = kv_streamed / hattn_avg_ms / 1e6 if hattn_avg_ms > 0 else 0.0
+    variant = "attn_partial_kernel<1,16,1>"
+    cpu = cpu_reference_time(min(args.steps, 20), min(args.warmup, 3), lens, budget_s=40.0) if world == 1 else None
+    # Secondary numbers, outside the timed regions of the headline.
     extend = measure_extend(dev, 10, 3) if world == 1 else None
     request_pool = measure_request_pool(dev, lens) if world == 1 else None
 
+    value = kv_all_ranks / ms_host / 1e6
     line = {
-        "metric": METRIC, "value": kv_all_ranks / ms_hbm / 1e6, "unit": UNIT, "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_hbm, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "opt-6.7b layer decode, 16 ragged requests ctx U[512,8192], 16-token permuted pages",
-                   "kv_bytes_per_step_per_gpu": kv_total, "tokens": sum(lens), "page_size": PAGE,
-                   "parallelism": f"head-shard x{world}: one 32-KV-head shard and one host pool per rank, no collective",
-                   "l2": "inputs larger than L2 (0.98 GB of KV per step vs 126 MB)",
-                   "value_mode": f"KV pool resident in HBM; the {args.steps} timed steps (4 launches each) are captured in one "
-                                 f"CUDA graph, as a model's layers are, and launched once (one graph launch per step: "
-                                 f"{ms_hbm_one:.4f} ms per step; eager launches: {ms_hbm_eager:.4f} ms per step)",
-                   "e2e_mode": "KV pool in pinned host memory, streamed over PCIe; eager calls of kernel.decode"},
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_host, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(world, lens),
+        "modes": {"value": "KV pool in pinned host memory, streamed over the host link by the kernel; X, Q, lengths on the "
+                           "device; eager calls of kernel.decode (4 launches per step)",
+                  "e2e": "the same plus per-step pinned host->device copies of X, Q and the lengths and the output back",
+                  "hbm": f"KV pool resident in HBM; {args.steps} steps per CUDA graph, {n_rep} replays timed one by one"},
+        "per_rank": {"kv_bytes_per_step": kv_total, "host_kv_gbs": host_rank_gbs, "streaming_kernel_gbs": attn_rank_gbs,
+                     "host_link_gbs": link_ranks},
         "e2e": {"value": kv_all_ranks / ms_e2e / 1e6, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": kv_streamed + x_pin.numel() * 2 + q_pin.numel() * 2 + len_pin.numel() * 4,
                 "d2h_bytes_per_step": out_pin.numel() * 2 + B * shape.nh_kv * 2 * 128 * 2,
-                "steps": e2e_steps},
-        "host_link": {"peak_gbs": link_gbs, "how": "pinned host->device copy of 1 GiB, best of 5, this run",
-                      "achieved_gbs": kv_total / ms_e2e / 1e6, "frac": kv_total / ms_e2e / 1e6 / link_gbs},
-        "roofline": {"kernel": "attn_partial_kernel", "bound": "hbm", "achieved": achieved, "peak": peak,
-                     "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes": kv_streamed,
-                     "avg_launch_ms": attn_avg_ms, "launches_timed": attn_n},
-        "gpu_launches": launches_hbm,
+                "steps": args.steps},
+        "roofline": {"kernel": variant, "bound": "host_link", "achieved": achieved_host, "peak": link_gbs,
+                     "peak_kind": "pinned host->device cudaMemcpyAsync of 1 GiB measured in this run, all ranks copying at "
+                                  "once behind a barrier (rank 0's median; per_rank.host_link_gbs has the spread)",
+                     "peak_best_copy": link_best, "unit": "GB/s", "frac": achieved_host / link_gbs,
+                     "per_rank": {k: attn_rank_gbs[k] / link_ranks[k2] for k, k2 in (("min", "max"), ("mean", "mean"), ("max", "min"))},
+                     "algorithmic_bytes": kv_streamed, "avg_launch_ms": attn_avg_ms, "launches_timed": attn_n,
+                     "traffic": HOST_TRAFFIC_BYTES_PER_LAUNCH if world == 1 and args.variant is None else None,
+                     "traffic_source": HOST_TRAFFIC_SOURCE if world == 1 and args.variant is None else
+                                       "none: the ncu capture belongs to the 1-GPU workload and the default kernel variant"},
+        "hbm": {"value": kv_all_ranks / ms_hbm / 1e6, "unit": UNIT, "ms_per_step": ms_hbm,
+                "ms_per_step_spread": {"min": reps[0], "median": ms_hbm_own, "max": reps[-1], "replays": n_rep,
+                                       "timed_region_s": hbm_total_s},
+                "ms_per_step_eager": ms_hbm_eager, "frac_of_8TBs": kv_all_ranks / ms_hbm / 1e6 / (8000.0 * world),
+                "roofline": {"kernel": variant, "bound": "hbm", "achieved": achieved_hbm, "peak": peak,
+                             "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved_hbm / peak,
+                             "algorithmic_bytes": kv_streamed, "avg_launch_ms": hattn_avg_ms, "launches_timed": hattn_n,
+                             "traffic": HBM_TRAFFIC_BYTES_PER_LAUNCH if world == 1 and args.variant is None else None,
+                             "traffic_source": HBM_TRAFFIC_SOURCE if world == 1 and args.variant is None else
+                                               "none: the ncu capture belongs to the 1-GPU workload and the default kernel variant"}},
+        "gpu_launches": launches_host,
         "clocks": clocks,
     }
+    if mg_check is not None:
+        line["multi_gpu_check"] = mg_check
+    if seq_split is not None:
+        line["seq_split"] = seq_split
     if extend is not None:
         line["extend"] = extend
     if request_pool is not None:
         line["e2e_request_pool"] = request_pool
-    if cpu_gbs is not None:
+    if cpu is not None:
+        cpu_gbs, cpu_ms, cores, sample, _ = cpu
         line["cpu_baseline"] = {"value": cpu_gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
                                 "ms_per_step": cpu_ms}
     print(json.dumps(line), flush=True)
@@ -695,9 +980,15 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM bytes (read 980.18 MB + write 5.03 MB) per launch of the streaming kernel on this workload, from the
-# ncu capture summarised in profiles/attn_partial_kernel_c2_hbm.md.
-TRAFFIC_BYTES_PER_LAUNCH = 985_208_320
+# Bytes per launch of the streaming kernel on the 1-GPU workload, from ncu captures of the default variant
+# (attn_partial_kernel<1,16,1>): with the pool in pinned host memory the traffic that matters crosses PCIe
+# (pcie__read_bytes.sum; DRAM sees 0.2-2 MB), with the pool in HBM it is dram__bytes_read.sum + dram__bytes_write.sum.
+HOST_TRAFFIC_BYTES_PER_LAUNCH = 1_071_760_000
+HOST_TRAFFIC_SOURCE = ("ncu pcie__read_bytes.sum of one launch (payload 977.6 MB + completion headers), "
+                       "`bench.py --only host`, -k regex:attn_partial -c 2, --clock-control none")
+HBM_TRAFFIC_BYTES_PER_LAUNCH = 985_208_320
+HBM_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum (980.18 MB) + dram__bytes_write.sum (5.03 MB) of one launch, "
+                      "`bench.py --only hbm`, -k regex:attn_partial -c 3, --clock-control none")
 
 if __name__ == "__main__":
     main()

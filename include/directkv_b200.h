@@ -324,8 +324,9 @@ typedef struct {
 
 int dkv_decode_noalloc(const dkv_noalloc_args* args, void* stream);
 
-/* Host-link helper: device-side copy kernel reading `bytes` from src (host-mapped or device)
- * into dst (device) with plain vector loads; used to measure the zero-copy roofline. */
+/* Measurement aid, not part of the drop-in surface (no counterpart in the reference): a device-side copy
+ * kernel reading `bytes` from src (host-mapped or device) into dst (device) with plain vector loads, to find
+ * what reads issued by the SMs reach over the host link of a given machine. */
 int dkv_stream_copy(dkv_context* ctx, void* dst, const void* src, int64_t bytes, void* stream);
 
 #ifdef __cplusplus

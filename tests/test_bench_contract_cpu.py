@@ -15,11 +15,12 @@ def test_reference_arm_prints_contract_line():
     lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
     assert len(lines) == 1
     d = json.loads(lines[0])
-    assert d["impl"] == "reference" and d["metric"] == "decode_attention_kv_gbps" and d["unit"] == "GB/s"
+    assert d["impl"] == "reference" and d["metric"] == "decode_attention_host_kv_gbps" and d["unit"] == "GB/s"
     assert d["higher_is_better"] is True and d["value"] > 0 and d["gpu_launches"] == 0
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
     assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
-    assert "workload" in d["config"]
+    assert "workload" in d["config"] and "parallelism" in d["config"]
+    assert d["steps"] == 1 and "all 16 requests" in d["cpu_baseline"]["sample"]
 
 
 def test_reference_arm_other_ranks_exit_quietly():

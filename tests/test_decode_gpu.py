@@ -145,18 +145,18 @@ def test_hbm_resident_pool():
 
 
 def test_config1_llama3_8b_layer():
-    """BASELINE config 1: Llama-3-8B layer, batch 1, 4096 cached tokens + the decoded one, RoPE theta 5e5."""
+    """Llama-3-8B layer, batch 1, 4096 cached tokens + the decoded one, RoPE theta 5e5."""
     _run_decode(workloads.LLAMA3_8B, [4097], 16, cfg_id=0)
 
 
 def test_config2_shape_opt67b_ragged_small():
-    """Config 2 geometry (32 MHA heads, hidden 4096, 16-token permuted pages, 16 ragged requests) at short lengths."""
+    """OPT-6.7B geometry (32 MHA heads, hidden 4096, 16-token permuted pages, 16 ragged requests) at short lengths."""
     lens = workloads.ragged_lengths_uniform(16, 8, 300, seed=4235)
     _run_decode(workloads.OPT_6_7B, lens, 16, cfg_id=1)
 
 
 def test_config5_shape_opt30b_shard():
-    """Config 5 geometry on one GPU of eight: 7 MHA heads, hidden 7168."""
+    """OPT-30B geometry on one GPU of eight: 7 MHA heads, hidden 7168."""
     _run_decode(workloads.OPT_30B.shard(8), [513, 1024, 37], 16, cfg_id=5)
 
 
@@ -221,8 +221,9 @@ def test_larger_ragged_batch_balance():
 
 
 def test_config2_full_size_properties():
-    """BASELINE config 2 at its full size (16 requests, ctx U[512,8192], 32 MHA heads, 16-token pages, about 1 GB
-    of KV, pool in HBM), checked through properties that do not need the CPU oracle at that size:
+    """The OPT-6.7B ragged batch at its full size (16 requests, ctx U[512,8192], 32 MHA heads, 16-token pages, about
+    1 GB of KV, pool in HBM), checked through properties that hold for every request at once (the comparison of
+    single requests with the oracle at this size is tests/test_fullsize_gpu.py):
       * doubling V doubles O bit-exactly (powers of two are exact in bf16 and fp32);
       * moving every page to another slot (a different permutation of the same logical contents) leaves O
         bit-identical: tiles, their order and every rounding point are the same;

@@ -57,6 +57,18 @@ def test_single_rank_exchange_matches_decode():
                           lse_out=lse)
         ctx.raise_on_status()
         assert_close(o, ref, f"world-1 exchange step {step}")
+    # 40 more steps without host synchronisation and with a different query each: consecutive steps alternate
+    # between the two halves of the record buffer and carry their own sequence number.
+    g = torch.Generator().manual_seed(5)
+    qs = torch.randn(40, 1, 8, 128, generator=g).to(torch.bfloat16)
+    qd, outs = qs.to(DEV), torch.empty(40, 1, 8, 128, dtype=torch.bfloat16, device=DEV)
+    for i in range(40):
+        kernel.decode(60, qd[i], case["seq_lens"], shape.scale, page_table=case["page_table"], exchange=h, out=outs[i])
+    ctx.raise_on_status()
+    for i in range(40):
+        ref_i = orc.decode_layer(None, None, None, qs[i], case["k_pool"].cpu(), case["v_pool"].cpu(),
+                                 case["page_table"].cpu(), [700], 16, None, shape.scale)
+        assert_close(outs[i], ref_i, f"world-1 exchange, unsynchronised step {i}")
     with pytest.raises(RuntimeError, match="max_rows"):
         q_big = torch.zeros(3, 8 * 128, dtype=torch.bfloat16, device=DEV)
         kernel.decode(60, q_big, torch.ones(3, dtype=torch.int32, device=DEV), shape.scale,

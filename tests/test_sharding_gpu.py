@@ -70,13 +70,26 @@ def _worker(rank, world, port):
         ex = sharding.PartialExchange(max_rows=64, device=rank)
         lens_dev = torch.tensor([e - s], dtype=torch.int32, device=dev)
         off_dev = torch.tensor([s], dtype=torch.int32, device=dev)
-        for it in range(3):                                   # repeated steps exercise the cumulative counters
-            lse = torch.empty(shape.nh_q, dtype=torch.float32, device=dev)
-            o2 = ex.decode(1, one["q"].to(dev), lens_dev, shape.scale, local_pages.to(dev),
-                           x=one["x"].to(dev) if is_owner else None, pos_offset=off_dev if is_owner else None, lse_out=lse)
-            torch.cuda.synchronize()
-            get_context(rank).raise_on_status()
-            assert_close(o2, ref1, f"exchange O (rank {rank}, step {it})")
+        # 200 steps back to back with NO host synchronisation between them and a different query in each: a rank
+        # may run a step ahead of its peer, so a record buffer that is reused too early, or a wait that lets a
+        # later step's records through, shows up as a wrong output of some step.
+        steps = 200
+        g = torch.Generator().manual_seed(77)
+        q_steps = torch.randn(steps, 1, shape.nh_q, 128, generator=g).to(torch.bfloat16)
+        q_dev = q_steps.to(dev)
+        outs = torch.empty(steps, 1, shape.nh_q, 128, dtype=torch.bfloat16, device=dev)
+        x_dev = one["x"].to(dev) if is_owner else None
+        pages_dev = local_pages.to(dev)
+        for it in range(steps):
+            kernel.decode(1, q_dev[it], lens_dev, shape.scale, page_table=pages_dev, x=x_dev,
+                          pos_offset=off_dev if is_owner else None, out=outs[it], exchange=ex.handle)
+        torch.cuda.synchronize()
+        get_context(rank).raise_on_status()
+        k_ref, v_ref = one["k_pool"].clone(), one["v_pool"].clone()
+        for it in range(steps):
+            ref_it = orc.decode_layer(one["x"], one["wk"], one["wv"], q_steps[it], k_ref, v_ref, one["page_table"], [n + 1],
+                                      16, one["cos_sin"], shape.scale)
+            assert_close(outs[it], ref_it, f"exchange O (rank {rank}, step {it} of {steps})")
         ex.close()
     finally:
         dist.destroy_process_group()
