@@ -510,6 +510,57 @@ def run_sweep(args, rank, world, local_rank, dev, dist):
 
 
 # ---------------------------------------------------------------------------------------------------
+# Serving-level simulation (the reference's benchmarks/bench_offload_serving.py and bench_offload_longctx.py
+# measure a served model over HTTP; here the attention backend is driven directly, see directkv_b200/serve_sim.py).
+# ---------------------------------------------------------------------------------------------------
+def serve_sim_configs():
+    """(name, layer shape, prompt lengths, churn, lengths of the requests that join) per benchmark configuration,
+    sized to what one request pool can hold: a pool row has the maximum context length, and the backend keeps at
+    most 64 rows, like the reference."""
+    c2 = workloads.ragged_lengths_uniform(16, 512, 8192, seed=4234 + CFG_ID)
+    c4 = workloads.ragged_lengths_lognormal(58, 8192, 1.0, 256, 16384, seed=4234 + 3)
+    c4_new = workloads.ragged_lengths_lognormal(48, 8192, 1.0, 256, 16384, seed=4234 + 20)
+    return [
+        ("C1 llama3-8b, 1 request, 4K prompt", workloads.LLAMA3_8B, [4096], 0.0, None),
+        ("C2 opt-6.7b, 16 requests, prompts U[512,8192]", workloads.OPT_6_7B, c2, 0.0, None),
+        ("C3 llama3-8b, 1 request, 32K prompt", workloads.LLAMA3_8B, [32768], 0.0, None),
+        ("C3 llama3-8b, 1 request, 128K prompt", workloads.LLAMA3_8B, [131072], 0.0, None),
+        ("C4 llama3-8b, 58 requests lognormal (median 8K, clipped to 16K), 10% replaced per step", workloads.LLAMA3_8B,
+         c4, 0.1, c4_new),
+        ("C5 opt-30b shard (7 of 56 heads), 32 requests, 16K prompts", workloads.OPT_30B.shard(8), [16384] * 32, 0.0, None),
+    ]
+
+
+def run_serve_sim(args, dev):
+    """bench.py --serve-sim [--serve-sim-out PATH]: one row per configuration and launch mode (eager steps, which
+    bring the rows in with the copy engines, and CUDA-graph replays, which stream them with the SMs) in the columns
+    of the reference's serving benchmark; prints the rows as JSON lines and appends them to the CSV."""
+    import csv
+
+    from directkv_b200 import serve_sim
+
+    only = set(args.serve_sim.split(",")) if args.serve_sim != "all" else None
+    rows = []
+    for name, shape, lens, churn, fresh in serve_sim_configs():
+        if only is not None and name.split()[0] not in only:
+            continue
+        for use_graph in (False, True):
+            r = serve_sim.run_config(name, shape, lens, dev, decode_steps=args.serve_sim_steps, churn=churn, fresh_lens=fresh,
+                                     use_graph=use_graph)
+            rows.append(r)
+            print(json.dumps(r), flush=True)
+    if args.serve_sim_out:
+        os.makedirs(os.path.dirname(args.serve_sim_out) or ".", exist_ok=True)
+        exists = os.path.exists(args.serve_sim_out)
+        with open(args.serve_sim_out, "a", newline="") as f:
+            w = csv.DictWriter(f, fieldnames=serve_sim.SERVING_CSV_HEADER, extrasaction="ignore")
+            if not exists:
+                w.writeheader()
+            for r in rows:
+                w.writerow({k: r.get(k, "") for k in serve_sim.SERVING_CSV_HEADER})
+
+
+# ---------------------------------------------------------------------------------------------------
 # Multi-GPU parts of the default run: parity on a small case, and the 1M-token sequence split.
 # ---------------------------------------------------------------------------------------------------
 def multi_gpu_check(rank, world, dev, dist):
@@ -685,6 +736,10 @@ def main():
     ap.add_argument("--longctx-csv", default=None,
                     help="with --sweep C3: also append rows in the column layout of the reference's long-context benchmark")
     ap.add_argument("--seq-split-ctx", type=int, default=1 << 20, help="context of the sequence-split arm (N > 1)")
+    ap.add_argument("--serve-sim", default=None,
+                    help="'all' or a comma list of C1..C5: run the serving-level simulation of those configurations instead")
+    ap.add_argument("--serve-sim-steps", type=int, default=12, help="decoded tokens per request in the simulation")
+    ap.add_argument("--serve-sim-out", default=None, help="CSV (columns of the reference's serving benchmark) to append to")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -742,6 +797,9 @@ def main():
 
     if args.only == "extend":
         run_extend_probe(args, dev)
+        return
+    if args.serve_sim:
+        run_serve_sim(args, dev)
         return
 
     full = workloads.OPT_6_7B

@@ -66,6 +66,23 @@ __device__ __forceinline__ WarpSplit warp_split(const AttnParams& p, long long U
     if (w.spread) w.qn = p.min_units;
     return w;
 }
+// Ring depth of a warp.  Normally every warp owns NST stages.  On a short step (spread mode) only the first few
+// warps of a CTA have work - warp w is active iff w * nctas + cta < (warps with work) - and the stages of the idle
+// ones would lie unused while an active warp waits for one tile at a time: a whole memory round trip per 16
+// tokens.  The active warps therefore share out all NWARPS * NST stages of the CTA (at most kMaxRingDepth each), so
+// that a warp has its whole unit range in flight at once.  Active warp w uses stages [w * depth, (w + 1) * depth).
+constexpr int kMaxRingDepth = 8;
+template <int NWARPS, int NST>
+__device__ __forceinline__ int ring_depth(const WarpSplit& w, long long U, int cta, int nctas) {
+    if (!w.spread) return NST;
+    const long long n_log = (U + w.qn - 1) / w.qn;                    // warps of the grid that have work
+    long long n_act = (n_log - cta + nctas - 1) / nctas;              // ... of this CTA: warps 0 .. n_act - 1
+    n_act = n_act < 1 ? 1 : (n_act > NWARPS ? NWARPS : n_act);
+    int depth = (NWARPS * NST) / static_cast<int>(n_act);
+    depth = depth > kMaxRingDepth ? kMaxRingDepth : depth;
+    return depth < NST ? NST : depth;
+}
+
 // Logical index (position of the warp's unit range, and of its partial record) of a physical warp.
 __device__ __forceinline__ int logical_warp(const WarpSplit& w, int cta, int warp, int nwarps, int nctas) {
     return w.spread ? warp * nctas + cta : cta * nwarps + warp;
@@ -245,8 +262,6 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g4 = lane >> 3, j = lane & 7;
-    uint8_t* wbase = smem + static_cast<size_t>(warp) * NST * kStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(NWARPS) * NST * kStageBytes) + warp * NST;
 
     const int nhs = p.nh_kv * p.nsub;
     const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
@@ -256,10 +271,12 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     const long long u0 = static_cast<long long>(gw) * qn;
     const long long u1 = (u0 + qn < U) ? u0 + qn : U;
     if (u0 >= u1) return;  // warps are independent: no CTA-wide barrier follows
+    const int depth = ring_depth<NWARPS, NST>(ws, U, blockIdx.x, gridDim.x);
+    uint8_t* wbase = smem + static_cast<size_t>(warp) * depth * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(NWARPS) * NST * kStageBytes) + warp * depth;
 
     if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < NST; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < depth; ++s) mbar_init(&bars[s], 1);
         fence_mbar_init();
         fence_proxy_async_smem();
         tma_prefetch_desc(&tmK);
@@ -269,18 +286,17 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
 
     TileCursor cc, pc;
     cc.locate(p, u0, nhs);
-    pc = cc;
-    long long pu = u0;  // next unit the producer will issue
-
-    // Prologue: fill the ring.
-#pragma unroll
-    for (int s = 0; s < NST; ++s) {
-        if (pu < u1) {
-            if (lane == 0) issue_tile(p, &tmK, &tmV, pc, wbase + s * kStageBytes, &bars[s]);
-            pc.advance(p, nhs);
-            ++pu;
-        }
+    // Prologue: lane s starts the copies of stage s, so the page-table reads of all stages of the ring are one
+    // round trip instead of a chain of them.
+    if (lane < depth && u0 + lane < u1) {
+        TileCursor c;
+        c.locate(p, u0 + lane, nhs);
+        issue_tile(p, &tmK, &tmV, c, wbase + lane * kStageBytes, &bars[lane]);
     }
+    long long pu = (u0 + depth < u1) ? u0 + depth : u1;  // next unit the producer (lane 0) will issue
+    pc = cc;
+    if (pu < u1) pc.locate(p, pu, nhs);
+    __syncwarp();
 
     uint32_t phase_bits = 0;  // bit s = parity to wait for on stage s
     int stage = 0;
@@ -401,7 +417,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
             pc.advance(p, nhs);
             ++pu;
         }
-        stage = (stage + 1 == NST) ? 0 : stage + 1;
+        stage = (stage + 1 == depth) ? 0 : stage + 1;
 
         // ---- end of this (request, head-slot) piece? ----
         const bool last_of_seg = (cc.tile + 1 == cc.tiles_b) || (u + 1 == u1);
@@ -443,7 +459,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     if (failed) {
         if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
         // Give copies still in flight a bounded chance to land before the stages are released.
-        for (int s = 0; s < NST; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
+        for (int s = 0; s < depth; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
     }
 }
 

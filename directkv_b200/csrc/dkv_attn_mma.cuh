@@ -92,8 +92,6 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r4 = lane >> 2, c4 = lane & 3;          // fragment row (and row + 8), column pair
-    uint8_t* wbase = smem + static_cast<size_t>(warp) * NST * kStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(NWARPS) * NST * kStageBytes) + warp * NST;
 
     const int G = p.g_total / p.nsub;                 // query rows per record, <= 16
     const bool hi_rows = G > 8;
@@ -105,10 +103,12 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const long long u0 = static_cast<long long>(gw) * qn;
     const long long u1 = (u0 + qn < U) ? u0 + qn : U;
     if (u0 >= u1) return;
+    const int depth = ring_depth<NWARPS, NST>(ws, U, blockIdx.x, gridDim.x);
+    uint8_t* wbase = smem + static_cast<size_t>(warp) * depth * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(NWARPS) * NST * kStageBytes) + warp * depth;
 
     if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < NST; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < depth; ++s) mbar_init(&bars[s], 1);
         fence_mbar_init();
         fence_proxy_async_smem();
         tma_prefetch_desc(&tmK);
@@ -118,16 +118,17 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 
     TileCursor cc, pc;
     cc.locate(p, u0, nhs);
-    pc = cc;
-    long long pu = u0;
-#pragma unroll
-    for (int s = 0; s < NST; ++s) {
-        if (pu < u1) {
-            if (lane == 0) issue_tile_sw(p, &tmK, &tmV, pc, wbase + s * kStageBytes, &bars[s]);
-            pc.advance(p, nhs);
-            ++pu;
-        }
+    // Prologue: lane s starts the copies of stage s, so the page-table reads of all stages of the ring are one
+    // round trip instead of a chain of them.
+    if (lane < depth && u0 + lane < u1) {
+        TileCursor c;
+        c.locate(p, u0 + lane, nhs);
+        issue_tile_sw(p, &tmK, &tmV, c, wbase + lane * kStageBytes, &bars[lane]);
     }
+    long long pu = (u0 + depth < u1) ? u0 + depth : u1;  // next unit the producer (lane 0) will issue
+    pc = cc;
+    if (pu < u1) pc.locate(p, pu, nhs);
+    __syncwarp();
 
     uint32_t phase_bits = 0;
     int stage = 0;
@@ -258,7 +259,7 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
             pc.advance(p, nhs);
             ++pu;
         }
-        stage = (stage + 1 == NST) ? 0 : stage + 1;
+        stage = (stage + 1 == depth) ? 0 : stage + 1;
 
         const bool last_of_seg = (cc.tile + 1 == cc.tiles_b) || (u + 1 == u1);
         if (last_of_seg) {
@@ -296,7 +297,7 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
 
     if (failed) {
         if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
-        for (int s = 0; s < NST; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
+        for (int s = 0; s < depth; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
     }
 }
 
@@ -328,8 +329,6 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r4 = lane >> 2, c4 = lane & 3;
-    uint8_t* wbase = smem + static_cast<size_t>(warp) * NST * kStageBytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(NWARPS) * NST * kStageBytes) + warp * NST;
 
     const int G = p.g_total / p.nsub;                 // query heads per record, <= 8
     const int nhs = p.nh_kv * p.nsub;
@@ -340,10 +339,12 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     const long long u0 = static_cast<long long>(gw) * qn;
     const long long u1 = (u0 + qn < U) ? u0 + qn : U;
     if (u0 >= u1) return;
+    const int depth = ring_depth<NWARPS, NST>(ws, U, blockIdx.x, gridDim.x);
+    uint8_t* wbase = smem + static_cast<size_t>(warp) * depth * kStageBytes;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(NWARPS) * NST * kStageBytes) + warp * depth;
 
     if (lane == 0) {
-#pragma unroll
-        for (int s = 0; s < NST; ++s) mbar_init(&bars[s], 1);
+        for (int s = 0; s < depth; ++s) mbar_init(&bars[s], 1);
         fence_mbar_init();
         fence_proxy_async_smem();
         tma_prefetch_desc(&tmK);
@@ -353,16 +354,17 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 
     TileCursor cc, pc;
     cc.locate(p, u0, nhs);
-    pc = cc;
-    long long pu = u0;
-#pragma unroll
-    for (int s = 0; s < NST; ++s) {
-        if (pu < u1) {
-            if (lane == 0) issue_tile_sw(p, &tmK, &tmV, pc, wbase + s * kStageBytes, &bars[s]);
-            pc.advance(p, nhs);
-            ++pu;
-        }
+    // Prologue: lane s starts the copies of stage s, so the page-table reads of all stages of the ring are one
+    // round trip instead of a chain of them.
+    if (lane < depth && u0 + lane < u1) {
+        TileCursor c;
+        c.locate(p, u0 + lane, nhs);
+        issue_tile_sw(p, &tmK, &tmV, c, wbase + lane * kStageBytes, &bars[lane]);
     }
+    long long pu = (u0 + depth < u1) ? u0 + depth : u1;  // next unit the producer (lane 0) will issue
+    pc = cc;
+    if (pu < u1) pc.locate(p, pu, nhs);
+    __syncwarp();
 
     uint32_t phase_bits = 0;
     int stage = 0;
@@ -476,7 +478,7 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             pc.advance(p, nhs);
             ++pu;
         }
-        stage = (stage + 1 == NST) ? 0 : stage + 1;
+        stage = (stage + 1 == depth) ? 0 : stage + 1;
 
         const bool last_of_seg = (cc.tile + 1 == cc.tiles_b) || (u + 1 == u1);
         if (last_of_seg) {
@@ -520,7 +522,7 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 
     if (failed) {
         if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
-        for (int s = 0; s < NST; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
+        for (int s = 0; s < depth; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
     }
 }
 

@@ -715,7 +715,8 @@ int build_layer(LayerState* L, const dkv_layer_desc* d) {
 // Projection of T rows of X with RoPE and write-back (tcgen05 kernel).
 int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int T, const int* tok_pos,
                       const int* tok_slot, bool store_pool, __nv_bfloat16* kv_new, float* splitk, cudaStream_t st,
-                      bool beside_streaming = false, void* k_dst = nullptr, void* v_dst = nullptr, long long n_slots_dst = 0) {
+                      bool beside_streaming = false, void* k_dst = nullptr, void* v_dst = nullptr, long long n_slots_dst = 0,
+                      const DecodePlace* place = nullptr) {
     // The swapped-operand kernel pays off where it runs UNDER the streaming kernel (the 16-warp CUDA-core form
     // leaves it registers and shared memory); alone, the 128-token-tile kernel with its deeper ring is faster.
     const bool small = T <= kPdMaxBatch && (ctx->proj_decode == 1 || (ctx->proj_decode < 0 && beside_streaming));
@@ -735,6 +736,7 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
     if (rc != DKV_OK) return rc;
     pp.tok_pos = tok_pos;
     pp.tok_slot = tok_slot;
+    if (place != nullptr) pp.place = *place;
     pp.cos_sin = L.d.cos_sin;
     pp.max_pos = L.d.max_pos;
     // The rows go to the layer's pool, or (k_dst given) to a staging copy of it whose slots tok_slot addresses.
@@ -1053,14 +1055,17 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
     prep.page_shift = L.page_shift;
     prep.row_stride = L.d.row_stride;
     prep.save = a->save_kv_cache;
+    if (a->new_mode == DKV_NEW_PROJECT) {
+        // The projection depends neither on the streamed attention nor on the prep kernel (it works out the new
+        // tokens' positions and slots itself): it runs on the context's side stream, forked before prep and
+        // joined before the merge, so a short step has it off the critical path from the start.
+        DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
+        DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+    }
     attn_prep_kernel<<<1, 256, 0, st>>>(prep);
     DKV_CUDA(cudaGetLastError());
     ctx->launches += 1 + (a->new_mode == DKV_NEW_GIVEN ? 1 : 0);
     if (a->new_mode == DKV_NEW_PROJECT) {
-        // The projection does not depend on the streamed attention: it runs on the context's side
-        // stream (forked after prep, joined before the merge) so the two overlap.
-        DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
-        DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
         const int g_total = a->nh_q / nh_kv;
         bool rows_on_host = L.pool_on_host;              // where the streaming kernel will read from
         if (a->kv_source_layer != 0) {
@@ -1074,8 +1079,19 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
         const bool beside = a->batch > 0 &&
                             ((!mma_form && G_form == 1 && effective_variant(ctx, 1) == 2) ||
                              (mma_form && G_form <= 8 && ctx->attn_mma8 != 0 && (ctx->attn_variant < 0 || ctx->attn_variant == 2)));
-        rc = launch_projection(ctx, L, a->x, a->batch, tok_pos, tok_slot, a->save_kv_cache != 0, kv_new,
-                               reinterpret_cast<float*>(base + sp.splitk), ctx->side, beside);
+        DecodePlace place{};
+        place.seq_lens = a->seq_lens;
+        place.page_table = a->page_table;
+        place.row_map = a->row_map;
+        place.pos_offset = a->pos_offset;
+        place.pt_stride = a->pt_stride;
+        place.pt_rows = a->pt_rows;
+        place.page_size = L.d.page_size;
+        place.page_shift = L.page_shift;
+        place.row_stride = L.d.row_stride;
+        place.save = a->save_kv_cache;
+        rc = launch_projection(ctx, L, a->x, a->batch, nullptr, nullptr, a->save_kv_cache != 0, kv_new,
+                               reinterpret_cast<float*>(base + sp.splitk), ctx->side, beside, nullptr, nullptr, 0, &place);
         if (rc != DKV_OK) return rc;
         DKV_CUDA(cudaEventRecord(ctx->ev_join, ctx->side));
     } else if (a->new_mode == DKV_NEW_GIVEN) {

@@ -28,6 +28,19 @@ constexpr int kProjTmemCols  = 256;
 constexpr int kProjAccStride = kProjBN + 4;           // floats between rows of the split-K sum tile
 constexpr int kProjHead      = 128;                   // head dimension (rows of Wk_h / Wv_h)
 
+// Where the one new token of each request of a DECODE step goes, worked out by the projection itself from the
+// call's own arguments (tok_pos / tok_slot are nullptr then): the kernel reads nothing that the prep kernel
+// writes, so the two start together instead of one after the other.  Same arithmetic as attn_prep_kernel.
+struct DecodePlace {
+    const int* seq_lens;           // [T] tokens of request t including the new one; nullptr: not a decode step
+    const int* page_table;         // [rows, pt_stride] or nullptr (contiguous rows)
+    const int* row_map;            // [T] or nullptr
+    const int* pos_offset;         // [T] added to the RoPE position, or nullptr
+    int pt_stride, pt_rows, page_size, page_shift;
+    long long row_stride;
+    int save;                      // store the token to the pool
+};
+
 struct ProjParams {
     int T;                         // tokens (rows of X)
     int H;                         // hidden size, multiple of 64
@@ -45,7 +58,33 @@ struct ProjParams {
     float* splitk_scratch;         // [split_k, tilesM, nh_kv, 128, 256] fp32
     unsigned int* tile_counters;   // [tilesM * nh_kv], zero between launches
     unsigned int* status;
+    DecodePlace place;
 };
+
+__device__ __forceinline__ bool proj_has_pos(const ProjParams& p) {
+    return p.tok_pos != nullptr || p.place.seq_lens != nullptr;
+}
+
+// Absolute (RoPE) position of token `tok`.
+__device__ __forceinline__ int proj_tok_pos(const ProjParams& p, int tok) {
+    if (p.tok_pos != nullptr) return p.tok_pos[tok];
+    return p.place.seq_lens[tok] - 1 + (p.place.pos_offset ? p.place.pos_offset[tok] : 0);
+}
+
+// Pool slot token `tok` is stored to, or -1.
+__device__ __forceinline__ long long proj_tok_slot(const ProjParams& p, int tok) {
+    if (p.tok_slot != nullptr) return p.tok_slot[tok];
+    const DecodePlace& d = p.place;
+    if (d.seq_lens == nullptr || !d.save) return -1;
+    const int pos = d.seq_lens[tok] - 1;
+    if (pos < 0) return -1;
+    const int row = d.row_map ? d.row_map[tok] : tok;
+    if (d.page_table == nullptr) return static_cast<long long>(row) * d.row_stride + pos;
+    const int pg = pos >> d.page_shift;
+    if (pg >= d.pt_stride || row < 0 || (d.pt_rows > 0 && row >= d.pt_rows)) return -1;   // reported by attn_prep_kernel
+    return (static_cast<long long>(d.page_table[static_cast<long long>(row) * d.pt_stride + pg]) << d.page_shift) +
+           (pos & (d.page_size - 1));
+}
 
 // MT = 128-token sub-tiles per CTA (1 or 2).  With two, a stage holds 32 KB of X next to the same 32 KB of
 // weights and both halves of the 512 TMEM columns are used, so the weights cross L2 -> SM once per 256 tokens:
@@ -261,8 +300,8 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         };
 
         int pos = -1;
-        if (lane_valid && p.cos_sin != nullptr && p.tok_pos != nullptr) {
-            pos = p.tok_pos[token];
+        if (lane_valid && p.cos_sin != nullptr && proj_has_pos(p)) {
+            pos = proj_tok_pos(p, token);
             if (pos < 0 || pos >= p.max_pos) {
                 atomicOr(p.status, kStatusBadPosition);
                 pos = -1;
@@ -311,7 +350,7 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             const uint4 w = *reinterpret_cast<const uint4*>(stage_out + r * 512 + ((lane ^ (r & 31)) << 4));
             if (p.kv_new != nullptr)
                 *reinterpret_cast<uint4*>(p.kv_new + (static_cast<size_t>(tok) * p.nh_kv + h) * 256 + lane * 8) = w;
-            const long long slot = p.tok_slot ? p.tok_slot[tok] : -1;
+            const long long slot = proj_tok_slot(p, tok);
             if (slot >= 0 && p.k_pool != nullptr) {
                 if (slot < p.n_slots) {
                     __nv_bfloat16* dst = (lane < 16 ? p.k_pool : p.v_pool) +

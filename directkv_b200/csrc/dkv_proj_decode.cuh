@@ -6,8 +6,11 @@
 //
 //   K_h^T[128 dims x N tokens] = Wk_h[128 x H] . X[N x H]^T        (bf16 x bf16 -> fp32 in TMEM)
 //
-// which shrinks a pipeline stage to 32 KB of weights + N x 128 B of activations.  Two stages, 128 threads
-// and under 96 registers per thread leave this CTA room beside a 16-warp streaming CTA (128 KB, 104
+// which shrinks the operands of one 64-column step to 32 KB of weights + N x 128 B of activations.  The ring is
+// cut finer still: a stage holds ONE of the two weight chunks (Wk_h or Wv_h, 16 KB) with the X chunk it is
+// multiplied by, so that within the same shared memory three to five stages are in flight while one is being
+// multiplied (with two 34 KB stages only one was, and a short step ran at a third of the HBM rate).  128
+// threads and under 96 registers per thread leave this CTA room beside a 16-warp streaming CTA (128 KB, 104
 // registers), so the projection runs under the attention kernel instead of in front of it.
 //
 // Same contract as proj_rope_kernel (ProjParams): round to bf16, rotate K at the token's absolute
@@ -19,8 +22,9 @@
 
 namespace dkv {
 
-constexpr int kPdStages    = 2;
+constexpr int kPdMaxStages = 5;
 constexpr int kPdWBytes    = kProjHead * kProjBK * 2;   // 16 KB: one 64-column chunk of Wk_h or Wv_h
+constexpr int kPdRingBytes = 96 * 1024;                 // what the ring may take beside a streaming CTA
 constexpr int kPdMaxTokens = 128;                       // tokens per CTA (N side of the product)
 constexpr int kPdMaxBatch  = 512;                       // larger batches use the 128-token-tile kernel
 constexpr int kPdChunkTok  = 32;                        // tokens per epilogue pass
@@ -28,12 +32,18 @@ constexpr int kPdAccStride = 132;                       // floats between token 
 constexpr int kPdCtrlBytes = 256;
 
 __host__ __device__ constexpr int pd_padded_tokens(int T) { return (T + 15) / 16 * 16; }
-__host__ __device__ constexpr int pd_stage_bytes(int n_pad) { return 2 * kPdWBytes + n_pad * 128; }
-__host__ __device__ constexpr size_t pd_smem_bytes(int n_pad) {
-    return static_cast<size_t>(kPdStages) * pd_stage_bytes(n_pad) + kPdCtrlBytes + 1024;
+__host__ __device__ constexpr int pd_stage_bytes(int n_pad) { return kPdWBytes + n_pad * 128; }   // one weight chunk + X chunk
+__host__ __device__ constexpr int pd_stages(int n_pad) {
+    return kPdRingBytes / pd_stage_bytes(n_pad) < kPdMaxStages ? kPdRingBytes / pd_stage_bytes(n_pad) : kPdMaxStages;
 }
-static_assert(2 * kPdChunkTok * kPdAccStride * 4 + kPdChunkTok * 512 <= kPdStages * pd_stage_bytes(16),
+__host__ __device__ constexpr size_t pd_smem_bytes(int n_pad) {
+    return static_cast<size_t>(pd_stages(n_pad)) * pd_stage_bytes(n_pad) + kPdCtrlBytes + 1024;
+}
+static_assert(pd_stages(kPdMaxTokens) >= 3 && pd_stages(16) == kPdMaxStages, "ring depth");
+static_assert(2 * kPdChunkTok * kPdAccStride * 4 + kPdChunkTok * 512 <= pd_stages(16) * pd_stage_bytes(16) &&
+              2 * kPdChunkTok * kPdAccStride * 4 + kPdChunkTok * 512 <= pd_stages(kPdMaxTokens) * pd_stage_bytes(kPdMaxTokens),
               "epilogue tiles must fit in the operand ring");
+static_assert((2 * kPdMaxStages + 1) * 8 + 16 <= kPdCtrlBytes, "control block");
 
 // grid (nh_kv, split_k, ceil(T / 128)), 128 threads: a CTA owns one KV head, one slice of the hidden dimension and
 // up to 128 tokens.  tmX has box {64, min(128, T padded to 16)}; tmWk/tmWv box {64, 128}.
@@ -47,12 +57,13 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
     const int n_pad = pd_padded_tokens(T_cta);                         // N of the product
     const int box_rows = p.T > kPdMaxTokens ? kPdMaxTokens : pd_padded_tokens(p.T);        // rows one TMA box of X brings
     const int stage_bytes = pd_stage_bytes(box_rows);
+    const int n_stages = pd_stages(box_rows);
     const int vcol = n_pad <= 64 ? 64 : 128;             // TMEM column of the V accumulator
     const uint32_t tmem_cols = 2u * vcol;
-    uint8_t* ctrl = smem + kPdStages * stage_bytes;
+    uint8_t* ctrl = smem + n_stages * stage_bytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);
-    uint64_t* empty_bar = full_bar + kPdStages;
-    uint64_t* accum_bar = empty_bar + kPdStages;
+    uint64_t* empty_bar = full_bar + kPdMaxStages;
+    uint64_t* accum_bar = empty_bar + kPdMaxStages;
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(accum_bar + 1);
     volatile int* flags = reinterpret_cast<volatile int*>(tmem_holder + 1);  // [0] abort, [1] is_last
 
@@ -64,8 +75,7 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
     const int nloc = c1 - c0;
 
     if (tid == 0) {
-#pragma unroll
-        for (int s = 0; s < kPdStages; ++s) {
+        for (int s = 0; s < n_stages; ++s) {
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
@@ -90,19 +100,19 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
     if (warp == 0) {
         if (lane == 0) {
             // ---------------- TMA producer ----------------
-            for (int i = 0; i < nloc; ++i) {
-                const int s = i % kPdStages;
-                if (i >= kPdStages && !mbar_wait_bounded(&empty_bar[s], ((i / kPdStages) - 1) & 1)) {
+            // Step j = 2 i + kv: chunk i of Wk_h (kv = 0) or Wv_h (kv = 1) and chunk i of X.
+            for (int j = 0; j < 2 * nloc; ++j) {
+                const int s = j % n_stages, round = j / n_stages;
+                if (round > 0 && !mbar_wait_bounded(&empty_bar[s], (round - 1) & 1)) {
                     atomicOr(p.status, kStatusWaitTimeout);
                     flags[0] = 1;
                     break;
                 }
                 uint8_t* st = smem + s * stage_bytes;
                 mbar_arrive_expect_tx(&full_bar[s], static_cast<uint32_t>(stage_bytes));
-                const int kc = (c0 + i) * kProjBK;
-                tma_load_2d(st, &tmWk, &full_bar[s], kc, h * kProjHead);
-                tma_load_2d(st + kPdWBytes, &tmWv, &full_bar[s], kc, h * kProjHead);
-                tma_load_2d(st + 2 * kPdWBytes, &tmX, &full_bar[s], kc, tok_base);   // rows past T read as zeros
+                const int kc = (c0 + (j >> 1)) * kProjBK;
+                tma_load_2d(st, (j & 1) ? &tmWv : &tmWk, &full_bar[s], kc, h * kProjHead);
+                tma_load_2d(st + kPdWBytes, &tmX, &full_bar[s], kc, tok_base);   // rows past T read as zeros
             }
         }
         __syncwarp();
@@ -111,9 +121,9 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
             // ---------------- MMA issuer ----------------
             const uint32_t idesc = umma_idesc_bf16_f32(kProjHead, n_pad);
             bool ok = true;
-            for (int i = 0; i < nloc; ++i) {
-                const int s = i % kPdStages;
-                if (!mbar_wait_bounded(&full_bar[s], (i / kPdStages) & 1)) {
+            for (int j = 0; j < 2 * nloc; ++j) {
+                const int s = j % n_stages, round = j / n_stages;
+                if (!mbar_wait_bounded(&full_bar[s], round & 1)) {
                     atomicOr(p.status, kStatusWaitTimeout);
                     flags[0] = 1;
                     ok = false;
@@ -121,15 +131,12 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
                 }
                 tc_fence_after_sync();
                 const uint32_t w_addr = smem_u32(smem + s * stage_bytes);
-                const uint64_t wk_desc = umma_desc_k_sw128(w_addr);
-                const uint64_t wv_desc = umma_desc_k_sw128(w_addr + kPdWBytes);
-                const uint64_t x_desc = umma_desc_k_sw128(w_addr + 2 * kPdWBytes);
+                const uint64_t w_desc = umma_desc_k_sw128(w_addr);
+                const uint64_t x_desc = umma_desc_k_sw128(w_addr + kPdWBytes);
+                const uint32_t d = tmem_base + ((j & 1) ? vcol : 0);
 #pragma unroll
-                for (int k4 = 0; k4 < kProjBK / 16; ++k4) {
-                    const uint32_t acc = (i > 0 || k4 > 0) ? 1u : 0u;
-                    umma_bf16_ss(tmem_base, wk_desc + 2 * k4, x_desc + 2 * k4, idesc, acc);
-                    umma_bf16_ss(tmem_base + vcol, wv_desc + 2 * k4, x_desc + 2 * k4, idesc, acc);
-                }
+                for (int k4 = 0; k4 < kProjBK / 16; ++k4)
+                    umma_bf16_ss(d, w_desc + 2 * k4, x_desc + 2 * k4, idesc, (j > 1 || k4 > 0) ? 1u : 0u);
                 umma_commit(&empty_bar[s]);
             }
             if (ok) umma_commit(accum_bar);
@@ -223,8 +230,8 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
                 if (tid < 64) {
                     float lo = round_bf16(sacc[r * kPdAccStride + tid]);
                     float hi = round_bf16(sacc[r * kPdAccStride + tid + 64]);
-                    if (p.cos_sin != nullptr && p.tok_pos != nullptr) {
-                        const int pos = p.tok_pos[tok];
+                    if (p.cos_sin != nullptr && proj_has_pos(p)) {
+                        const int pos = proj_tok_pos(p, tok);
                         if (pos >= 0 && pos < p.max_pos) {
                             const float* cs = p.cos_sin + static_cast<size_t>(pos) * kProjHead;
                             const float cv = __ldg(cs + tid), sv = __ldg(cs + 64 + tid);
@@ -250,7 +257,7 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
                 const uint4 w = *reinterpret_cast<const uint4*>(stage_out + r * 512 + lane * 16);
                 if (p.kv_new != nullptr)
                     *reinterpret_cast<uint4*>(p.kv_new + (static_cast<size_t>(tok) * p.nh_kv + h) * 256 + lane * 8) = w;
-                const long long slot = p.tok_slot ? p.tok_slot[tok] : -1;
+                const long long slot = proj_tok_slot(p, tok);
                 if (slot >= 0 && p.k_pool != nullptr) {
                     if (slot < p.n_slots) {
                         __nv_bfloat16* dst = (lane < 16 ? p.k_pool : p.v_pool) +
