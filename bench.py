@@ -546,7 +546,7 @@ def run_serve_sim(args, dev):
             continue
         for use_graph in (False, True):
             r = serve_sim.run_config(name, shape, lens, dev, decode_steps=args.serve_sim_steps, churn=churn, fresh_lens=fresh,
-                                     use_graph=use_graph)
+                                     use_graph=use_graph, check_each_step=os.environ.get("DIRECTKV_B200_SIM_CHECK") == "1")
             rows.append(r)
             print(json.dumps(r), flush=True)
     if args.serve_sim_out:

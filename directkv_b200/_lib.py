@@ -33,6 +33,11 @@ STATUS_BITS = {
     1 << 3: "the tensor-core completion barrier ran out of time",
     1 << 4: "the sequence-split exchange found a record of another step (the ranks' calls do not line up)",
     1 << 5: "a sequence length or row led outside the page table",
+    1 << 8: "(in the KV-streaming kernel)",
+    1 << 9: "(in the projection's load pipeline)",
+    1 << 10: "(in the projection's tensor-core pipeline)",
+    1 << 11: "(in the extend attention kernel)",
+    1 << 12: "(in the sequence-split exchange)",
 }
 
 PARTIAL_STRIDE = 132  # floats per unnormalised partial row: O[128], m (log2 domain), l, 2 pad

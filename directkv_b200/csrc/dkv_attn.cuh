@@ -457,7 +457,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     }
 
     if (failed) {
-        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout | kStatusInStreaming);
         // Give copies still in flight a bounded chance to land before the stages are released.
         for (int s = 0; s < depth; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
     }
@@ -498,12 +498,17 @@ struct MergeParams {
 constexpr int kMergeThreads = 256;
 constexpr int kMergeBlock = 8;       // records loaded together
 
+// WPR = 32 (a CTA of 1024 threads on one row) is for a single very long request: one record per warp of the
+// streaming grid means about 300 per row at 128K tokens.
+constexpr int merge_threads(int wpr) { return wpr > kMergeThreads / 32 ? wpr * 32 : kMergeThreads; }
+
 template <int WPR>
-__global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const MergeParams mp) {
+__global__ void __launch_bounds__(merge_threads(WPR)) attn_merge_kernel(const MergeParams mp) {
+    constexpr int kThreads = merge_threads(WPR);
     const AttnParams& p = mp.a;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int part = warp % WPR, row_in_cta = warp / WPR;
-    const long long wid = static_cast<long long>(blockIdx.x) * (kMergeThreads / 32 / WPR) + row_in_cta;
+    const long long wid = static_cast<long long>(blockIdx.x) * (kThreads / 32 / WPR) + row_in_cta;
     const bool row_valid = wid < static_cast<long long>(p.batch) * p.nh_q;
     if (WPR == 1 && !row_valid) return;
     const int b = row_valid ? static_cast<int>(wid / p.nh_q) : 0, hq = row_valid ? static_cast<int>(wid % p.nh_q) : 0;
@@ -562,8 +567,8 @@ __global__ void __launch_bounds__(kMergeThreads) attn_merge_kernel(const MergePa
     }
 
     if (WPR > 1) {
-        __shared__ float4 s_acc[kMergeThreads / 32][32];
-        __shared__ float2 s_ml[kMergeThreads / 32];
+        __shared__ float4 s_acc[kThreads / 32][32];
+        __shared__ float2 s_ml[kThreads / 32];
         s_acc[warp][lane] = acc;
         if (lane == 0) s_ml[warp] = make_float2(m, l);
         __syncthreads();
@@ -715,7 +720,7 @@ __global__ void __launch_bounds__(128) merge_exchange_kernel(const ExchangeMerge
     }
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) {
-        if (lane == 0) atomicOr(ep.status, kStatusWaitTimeout);
+        if (lane == 0) atomicOr(ep.status, kStatusWaitTimeout | kStatusInExchange);
         return;
     }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);

@@ -296,7 +296,7 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     }
 
     if (failed) {
-        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout | kStatusInStreaming);
         for (int s = 0; s < depth; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
     }
 }
@@ -521,7 +521,7 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     }
 
     if (failed) {
-        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+        if (lane == 0) atomicOr(p.status, kStatusWaitTimeout | kStatusInStreaming);
         for (int s = 0; s < depth; ++s) (void)mbar_wait_bounded(&bars[s], (phase_bits >> s) & 1u);
     }
 }

@@ -21,6 +21,12 @@ enum StatusBits : unsigned int {
     kStatusTmemTimeout   = 1u << 3,   // the MMA-completion barrier ran out of time
     kStatusExchangeOrder = 1u << 4,   // sequence-split exchange: a record of another step was found
     kStatusBadPage       = 1u << 5,   // a page-table index lay outside the table
+    // Which kernel gave up waiting (set together with kStatusWaitTimeout / kStatusTmemTimeout).
+    kStatusInStreaming   = 1u << 8,   // KV-streaming kernel: a tile's copy did not arrive
+    kStatusInProjLoad    = 1u << 9,   // projection: the producer found no free stage
+    kStatusInProjMma     = 1u << 10,  // projection: the issuer's operands did not arrive, or the accumulator never completed
+    kStatusInExtend      = 1u << 11,  // extend attention kernel
+    kStatusInExchange    = 1u << 12,  // sequence-split exchange: a peer's records did not arrive
 };
 
 // Upper bound for any device-side wait, in nanoseconds of %globaltimer.

@@ -258,7 +258,7 @@ extend_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     ok = __syncthreads_and(ok);
     if (!ok) {
-        if (tid == 0) atomicOr(p.status, kStatusWaitTimeout);
+        if (tid == 0) atomicOr(p.status, kStatusWaitTimeout | kStatusInExtend);
     } else if (my_tok < p.S_new) {
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const int g = row % G;

@@ -130,7 +130,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             for (int q = 0; q < 2 * n_max; ++q) {             // q even: K(q/2), odd: V(q/2)
                 const int s = q % kPpSlots;
                 if (q >= kPpSlots && !mbar_wait_bounded(&ctl->empty[s], ((q / kPpSlots) - 1) & 1)) {
-                    atomicOr(p.status, kStatusWaitTimeout);
+                    atomicOr(p.status, kStatusWaitTimeout | kStatusInExtend);
                     ctl->abort = 1;
                     break;
                 }
@@ -141,6 +141,14 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 mbar_arrive_expect_tx(&ctl->full[s], kExtTileBytes);
                 tma_load_3d(dst, tm, &ctl->full[s], 0, h, slot);
                 tma_load_3d(dst + kExtHalfBytes, tm, &ctl->full[s], 64, h, slot);
+                // A slot is released by one arrival per query tile.  A tile that walks fewer keys than the other (or
+                // none: tile 1 past the last new row) never reads this K/V tile, and the producer - the one thread that
+                // follows every phase of the slot in order - arrives in its place.  (The tile's own issuer must not do
+                // it from a loop that runs ahead of the loads: it sees only every other phase of a slot, K and V
+                // alternate there, and a parity wait on a barrier that is a phase behind returns at once.)
+#pragma unroll
+                for (int g = 0; g < 2; ++g)
+                    if ((q >> 1) >= ((n_half[g] + 1) >> 1)) mbar_arrive(&ctl->empty[s]);
             }
         }
         __syncwarp();
@@ -176,13 +184,8 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 umma_commit(&ctl->bar_s[g][t & 1]);
                 if ((t & 1) || t == n_g - 1) umma_commit(&ctl->empty[slot]);   // this tile's last read of K(t >> 1)
             }
-            // K tiles the other query tile still reads: every ring slot expects one arrival per query tile.
-            for (int q = 2 * ((n_g + 1) >> 1); ok && q < 2 * n_max; q += 2) {
-                ok = mbar_wait_bounded(&ctl->full[q % kPpSlots], (q / kPpSlots) & 1);
-                if (ok) mbar_arrive(&ctl->empty[q % kPpSlots]);
-            }
             if (!ok) {
-                atomicOr(p.status, kStatusWaitTimeout);
+                atomicOr(p.status, kStatusWaitTimeout | kStatusInExtend);
                 ctl->abort = 1;
             }
         }
@@ -210,12 +213,8 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                 umma_commit(&ctl->bar_o[g][t & 1]);
                 if ((t & 1) || t == n_g - 1) umma_commit(&ctl->empty[slot]);
             }
-            for (int q = 2 * ((n_g + 1) >> 1) + 1; ok && q < 2 * n_max; q += 2) {
-                ok = mbar_wait_bounded(&ctl->full[q % kPpSlots], (q / kPpSlots) & 1);
-                if (ok) mbar_arrive(&ctl->empty[q % kPpSlots]);
-            }
             if (!ok) {
-                atomicOr(p.status, kStatusWaitTimeout);
+                atomicOr(p.status, kStatusWaitTimeout | kStatusInExtend);
                 ctl->abort = 1;
             }
         }
@@ -374,7 +373,7 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             tc_fence_after_sync();
         }
         if (!ok) {
-            if (lane == 0) atomicOr(p.status, kStatusWaitTimeout);
+            if (lane == 0) atomicOr(p.status, kStatusWaitTimeout | kStatusInExtend);
             ctl->abort = 1;
         } else if (n_g > 0) {
             const float inv = l > 0.f ? 1.f / l : 0.f;

@@ -144,7 +144,7 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             for (int i = 0; i < nloc; ++i) {
                 const int s = i % NST;
                 if (i >= NST && !mbar_wait_bounded(&empty_bar[s], ((i / NST) - 1) & 1)) {
-                    atomicOr(p.status, kStatusWaitTimeout);
+                    atomicOr(p.status, kStatusWaitTimeout | kStatusInProjLoad);
                     flags[0] = 1;
                     break;
                 }
@@ -165,7 +165,7 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             for (int i = 0; i < nloc; ++i) {
                 const int s = i % NST;
                 if (!mbar_wait_bounded(&full_bar[s], (i / NST) & 1)) {
-                    atomicOr(p.status, kStatusWaitTimeout);
+                    atomicOr(p.status, kStatusWaitTimeout | kStatusInProjMma);
                     flags[0] = 1;
                     ok = false;
                     break;
@@ -192,7 +192,7 @@ proj_rope_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(accum_bar, 0));
     tc_fence_after_sync();
     if (!ok && lane == 0) {
-        atomicOr(p.status, kStatusTmemTimeout);
+        atomicOr(p.status, kStatusTmemTimeout | kStatusInProjMma);
         flags[0] = 1;
     }
     __syncthreads();

@@ -104,7 +104,7 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
             for (int j = 0; j < 2 * nloc; ++j) {
                 const int s = j % n_stages, round = j / n_stages;
                 if (round > 0 && !mbar_wait_bounded(&empty_bar[s], (round - 1) & 1)) {
-                    atomicOr(p.status, kStatusWaitTimeout);
+                    atomicOr(p.status, kStatusWaitTimeout | kStatusInProjLoad);
                     flags[0] = 1;
                     break;
                 }
@@ -124,7 +124,7 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
             for (int j = 0; j < 2 * nloc; ++j) {
                 const int s = j % n_stages, round = j / n_stages;
                 if (!mbar_wait_bounded(&full_bar[s], round & 1)) {
-                    atomicOr(p.status, kStatusWaitTimeout);
+                    atomicOr(p.status, kStatusWaitTimeout | kStatusInProjMma);
                     flags[0] = 1;
                     ok = false;
                     break;
@@ -149,7 +149,7 @@ proj_rope_decode_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
     bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(accum_bar, 0));
     tc_fence_after_sync();
     if (!ok && lane == 0) {
-        atomicOr(p.status, kStatusTmemTimeout);
+        atomicOr(p.status, kStatusTmemTimeout | kStatusInProjMma);
         flags[0] = 1;
     }
     __syncthreads();

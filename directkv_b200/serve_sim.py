@@ -106,6 +106,17 @@ def make_batch(mode, seq_lens, req_ids, device, extend_lens=None, prefix_lens=No
 
 
 # --------------------------------------------------------------------------- the simulation
+def _host_memory_available() -> Optional[int]:
+    try:
+        with open("/proc/meminfo") as f:
+            for line in f:
+                if line.startswith("MemAvailable:"):
+                    return int(line.split()[1]) * 1024
+    except OSError:
+        pass
+    return None
+
+
 def _pct(xs: Sequence[float], q: float) -> float:
     xs = sorted(xs)
     return xs[min(len(xs) - 1, int(round(q * (len(xs) - 1))))]
@@ -238,7 +249,7 @@ class ServeSim:
 
 def run_config(name: str, shape: LayerShape, ctx_lens: Sequence[int], device, decode_steps: int = 12, churn: float = 0.0,
                fresh_lens: Optional[Sequence[int]] = None, use_graph: bool = False, layers: int = 4, layer_repeats: int = 8,
-               chunk: int = 4096, seed: int = 0) -> dict:
+               chunk: int = 4096, seed: int = 0, check_each_step: bool = False) -> dict:
     """Prefills ``ctx_lens`` requests, then decodes ``decode_steps`` tokens for the whole batch; with ``churn`` that
     fraction of the requests is replaced before every step after the first by new ones (lengths from
     ``fresh_lens`` in turn), whose prefill counts as their time to first token.  Returns one row in the reference's
@@ -248,15 +259,34 @@ def run_config(name: str, shape: LayerShape, ctx_lens: Sequence[int], device, de
     dev = torch.device(device)
     n_req = len(ctx_lens)
     max_ctx = max(list(ctx_lens) + list(fresh_lens or [0])) + decode_steps + 64
+    # The request pool is page-locked host memory: refuse a configuration that would take more than half of what
+    # the machine has free rather than push it into swapping.
+    pool_bytes = 2 * layers * (min(n_req + 1, 64) + 1) * (-(-max_ctx // 64) * 64) * shape.nh_kv * 128 * 2
+    avail = _host_memory_available()
+    if avail is not None and pool_bytes > avail // 2:
+        raise RuntimeError(f"serve_sim: the request pool of '{name}' needs {pool_bytes / 2**30:.1f} GiB of pinned host memory, "
+                           f"more than half of the {avail / 2**30:.1f} GiB available")
     sim = ServeSim(shape, max_reqs=n_req + 1, context_len=max_ctx, device=dev, layers=layers, layer_repeats=layer_repeats,
                    chunk=chunk, seed=seed)
+    sim.prefill(n_req, 16)                        # untimed: allocates the pool, registers the layers, first launches
+    sim.lengths.pop(n_req, None)                  # (its row is released at the first decode step, where it is absent)
     ttft = []
     rids = list(range(n_req))
     for rid, n in zip(rids, ctx_lens):
         ttft.append(sim.prefill(rid, int(n)))
     step = sim.decode_step_graph if use_graph else sim.decode_step
+    ctx = get_context(dev.index)
+
+    def check(what):
+        if check_each_step:                       # find the step a device-side failure belongs to (synchronises)
+            st = ctx.read_status(clear=False)
+            if st:
+                raise RuntimeError(f"serve_sim: device status {st:#x} after {what}")
+
+    check("the prefill of the batch")
     step(rids)                                    # untimed warm-up step (graph capture, first-use set-up)
-    tpot, next_rid, fresh_i = [], n_req, 0
+    check("the warm-up decode step")
+    tpot, next_rid, fresh_i = [], n_req + 1, 0
     g = torch.Generator().manual_seed(99 + seed)
     n_swap = int(round(churn * n_req))
     for s in range(decode_steps):
@@ -267,10 +297,12 @@ def run_config(name: str, shape: LayerShape, ctx_lens: Sequence[int], device, de
                 sim.lengths.pop(old, None)
                 rids[i] = next_rid
                 ttft.append(sim.prefill(next_rid, int(fresh_lens[fresh_i % len(fresh_lens)])))
+                check(f"the prefill of request {next_rid} ({fresh_lens[fresh_i % len(fresh_lens)]} tokens) before step {s}")
                 next_rid += 1
                 fresh_i += 1
         tpot.append(step(rids))
-    get_context(dev.index).raise_on_status()
+        check(f"decode step {s}")
+    ctx.raise_on_status()
     mean = statistics.mean(tpot)
     layers_total = layers * layer_repeats
     row = {

@@ -43,6 +43,12 @@ extern "C" {
 #define DKV_STATUS_TMEM_TIMEOUT  (1u << 3)
 #define DKV_STATUS_EXCHANGE_ORDER (1u << 4)  /* dkv_decode_exchange: a record of another step arrived (calls of the ranks do not line up) */
 #define DKV_STATUS_BAD_PAGE      (1u << 5)  /* a length or row led outside the page table; the entry was not read */
+/* Set together with a timeout bit: the kernel that gave up waiting. */
+#define DKV_STATUS_IN_STREAMING  (1u << 8)
+#define DKV_STATUS_IN_PROJ_LOAD  (1u << 9)
+#define DKV_STATUS_IN_PROJ_MMA   (1u << 10)
+#define DKV_STATUS_IN_EXTEND     (1u << 11)
+#define DKV_STATUS_IN_EXCHANGE   (1u << 12)
 
 /* How the token decoded in this step enters dkv_decode. */
 #define DKV_NEW_NONE     0   /* every attended token is already in the pool */

@@ -290,6 +290,44 @@ def test_extend_ragged_batch(host):
     kernel.unregister_layer(73)
 
 
+@pytest.mark.parametrize("s_new,past", [(1105, 4096), (1487, 6144), (70, 2048)])
+def test_back_to_back_extends_when_the_second_query_tile_is_empty(s_new, past):
+    """The last pair of query tiles of a chunk may hold only ONE tile (here s_new leaves fewer than 32 rows for the
+    pair with 4 query heads per KV head), which then reads no key at all while its partner walks past + s_new of
+    them.  Several layers' calls are issued back to back without host synchronisation, as a model does: every output
+    must match the oracle and no wait may run out."""
+    nh_q, nh_kv, H, layers = 8, 2, 256, 4
+    s_pad = past + s_new + 23
+    g = torch.Generator().manual_seed(977)
+    X = torch.randn(s_new, H, generator=g).to(torch.bfloat16)
+    Q = torch.randn(s_new, nh_q, 128, generator=g).to(torch.bfloat16)
+    cs = orc.build_cos_sin(s_pad, 128, 10000.0)
+    Xd, Qd = X.to(DEV), Q.to(DEV)
+    pools, weights = [], []
+    for li in range(layers):
+        Wk = (torch.randn(nh_kv, 128, H, generator=g) * 0.05).to(torch.bfloat16)
+        Wv = (torch.randn(nh_kv, 128, H, generator=g) * 0.05).to(torch.bfloat16)
+        K = (torch.randn(1, s_pad, nh_kv, 128, generator=g) * 0.4).to(torch.bfloat16)
+        V = (torch.randn(1, s_pad, nh_kv, 128, generator=g) * 0.4).to(torch.bfloat16)
+        Kd, Vd = K.clone().pin_memory(), V.clone().pin_memory()
+        kernel.register_layer(80 + li, Kd, Vd, Wk.to(DEV), Wv.to(DEV), cs.to(DEV), row_stride=s_pad)
+        pools.append((K, V, Kd, Vd))
+        weights.append((Wk, Wv))
+    outs = []
+    for rep in range(3):
+        for li in range(layers):
+            outs.append(kernel.extend_ragged(80 + li, Xd, Qd, [s_new], [past], [0], SCALE, True))
+    get_context(0).raise_on_status()
+    for li in range(layers):
+        K, V, Kd, Vd = pools[li]
+        kb, vb = K[:, :past + s_new].clone(), V[:, :past + s_new].clone()
+        ref = orc.smpv2_fwd(X.unsqueeze(0), weights[li][0], weights[li][1], Q.unsqueeze(0), kb, vb, cs, SCALE, True, past)
+        for rep in range(3):
+            assert_close(outs[rep * layers + li], ref[0], f"O of layer {li}, pass {rep}")
+        assert_close(Kd[0, past:past + s_new], kb[0, past:], "K write-back", atol=KV_ATOL, rtol=1e-2)
+        kernel.unregister_layer(80 + li)
+
+
 def test_extend_ragged_attend_paged():
     """Rows already stored in a token pool (page size 1): ragged attention through the page table."""
     nh_q, nh_kv = 8, 2
