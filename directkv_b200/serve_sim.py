@@ -261,13 +261,16 @@ def run_config(name: str, shape: LayerShape, ctx_lens: Sequence[int], device, de
     max_ctx = max(list(ctx_lens) + list(fresh_lens or [0])) + decode_steps + 64
     # The request pool is page-locked host memory: refuse a configuration that would take more than half of what
     # the machine has free rather than push it into swapping.
-    pool_bytes = 2 * layers * (min(n_req + 1, 64) + 1) * (-(-max_ctx // 64) * 64) * shape.nh_kv * 128 * 2
+    n_swap = int(round(churn * n_req)) if fresh_lens else 0
+    pool_rows = min(n_req + n_swap + 1, 64) + 1
+    pool_bytes = 2 * layers * pool_rows * (-(-max_ctx // 64) * 64) * shape.nh_kv * 128 * 2
     avail = _host_memory_available()
     if avail is not None and pool_bytes > avail // 2:
         raise RuntimeError(f"serve_sim: the request pool of '{name}' needs {pool_bytes / 2**30:.1f} GiB of pinned host memory, "
                            f"more than half of the {avail / 2**30:.1f} GiB available")
-    sim = ServeSim(shape, max_reqs=n_req + 1, context_len=max_ctx, device=dev, layers=layers, layer_repeats=layer_repeats,
-                   chunk=chunk, seed=seed)
+    # Rows: the batch, the requests that join before those they replace are seen to be gone, and the warm-up request.
+    sim = ServeSim(shape, max_reqs=n_req + n_swap + 1, context_len=max_ctx, device=dev, layers=layers,
+                   layer_repeats=layer_repeats, chunk=chunk, seed=seed)
     sim.prefill(n_req, 16)                        # untimed: allocates the pool, registers the layers, first launches
     sim.lengths.pop(n_req, None)                  # (its row is released at the first decode step, where it is absent)
     ttft = []
@@ -288,7 +291,6 @@ def run_config(name: str, shape: LayerShape, ctx_lens: Sequence[int], device, de
     check("the warm-up decode step")
     tpot, next_rid, fresh_i = [], n_req + 1, 0
     g = torch.Generator().manual_seed(99 + seed)
-    n_swap = int(round(churn * n_req))
     for s in range(decode_steps):
         if s and n_swap and fresh_lens:
             for i in torch.randperm(n_req, generator=g)[:n_swap].tolist():
