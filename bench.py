@@ -339,6 +339,50 @@ def measure_request_pool(dev, lens, steps=5, warmup=2):
     return res
 
 
+SHORT_CASES = {
+    "llama4k": ("llama3-8b layer, one request of 4096 stored tokens", workloads.LLAMA3_8B, [4097]),
+    "opt4k": ("opt-6.7b layer, one request of 4096 stored tokens", workloads.OPT_6_7B, [4097]),
+    "llama16k": ("llama3-8b layer, one request of 16384 stored tokens", workloads.LLAMA3_8B, [16385]),
+    "llama128k": ("llama3-8b layer, one request of 131072 stored tokens", workloads.LLAMA3_8B, [131073]),
+    "llama4x4k": ("llama3-8b layer, four requests of 4096 stored tokens", workloads.LLAMA3_8B, [4097] * 4),
+}
+
+
+def run_short_probe(args, dev):
+    """--only short-<case>: a short decode step with the pool in HBM, where the step is launch structure and latency
+    rather than bandwidth.  Twelve eager steps (what a profiler capture of this command sees), then the step time
+    from a CUDA graph of 20 steps (median of 7 replays), with and without the projection of the new token."""
+    from directkv_b200 import kernel
+    from directkv_b200._lib import get_context
+
+    label, shape, lens = SHORT_CASES[args.only[len("short-"):]]
+    case = workloads.make_decode_case(shape, lens, PAGE, 0, dev, kv_on_host=False)
+    kernel.register_layer(3, case["k_pool"], case["v_pool"], case["wk"], case["wv"], case["cos_sin"], page_size=PAGE,
+                          device=dev.index)
+    out = torch.empty_like(case["q"])
+
+    def full():
+        kernel.decode(3, case["q"], case["seq_lens"], shape.scale, page_table=case["page_table"], x=case["x"], out=out)
+
+    def attention_only():
+        kernel.decode(3, case["q"], case["seq_lens"], shape.scale, page_table=case["page_table"], out=out)
+
+    for _ in range(12):
+        full()
+    torch.cuda.synchronize()
+    get_context(dev.index).raise_on_status()
+    res = {}
+    for name, fn in (("step_us", full), ("attention_only_us", attention_only)):
+        replay = _graphed(fn, 20)
+        med, _ = _median_ms(replay, 7, 2, torch.cuda.synchronize)
+        res[name] = med / 20 * 1e3
+    get_context(dev.index).raise_on_status()
+    kvb = workloads.kv_bytes(shape, lens)
+    print(json.dumps({"metric": "short_decode_step_us", "unit": "us", "value": res["step_us"], "config": {"workload": label},
+                      "attention_only_us": res["attention_only_us"], "kv_gbs": kvb / res["step_us"] / 1e3,
+                      "frac_of_8TBs": kvb / res["step_us"] / 1e3 / 8000.0, "partial": "short decode step, pool in HBM"}))
+
+
 def run_extend_probe(args, dev):
     r = measure_extend(dev, max(3, min(args.steps, 20)), args.warmup)
     print(json.dumps({"metric": "extend_attention_tflops", "value": r["attention_tflops"], "unit": "TFLOP/s",
@@ -728,9 +772,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--variant", type=int, default=None, help="override the streaming-kernel variant")
-    ap.add_argument("--only", default="all", choices=["all", "hbm", "host", "extend"],
+    ap.add_argument("--only", default="all", choices=["all", "hbm", "host", "extend"] + ["short-" + k for k in SHORT_CASES],
                     help="hbm / host: time only that mode of the decode step; extend: time the chunked-prefill path "
-                         "(Llama-3-8B layer, 4096 new tokens) - short runs for profiler captures")
+                         "(Llama-3-8B layer, 4096 new tokens); short-<case>: a short decode step with the pool in HBM - "
+                         "short runs for profiler captures")
     ap.add_argument("--sweep", default=None, help="comma list of C1,C2,C3,C4,C5: run those configurations instead")
     ap.add_argument("--sweep-out", default="sweep.jsonl")
     ap.add_argument("--longctx-csv", default=None,
@@ -797,6 +842,9 @@ def main():
 
     if args.only == "extend":
         run_extend_probe(args, dev)
+        return
+    if args.only.startswith("short-"):
+        run_short_probe(args, dev)
         return
     if args.serve_sim:
         run_serve_sim(args, dev)
@@ -990,7 +1038,7 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(world, lens),
         "modes": {"value": "KV pool in pinned host memory, streamed over the host link by the kernel; X, Q, lengths on the "
-                           "device; eager calls of kernel.decode (4 launches per step)",
+                           f"device; eager calls of kernel.decode ({launches_host // max(args.steps, 1)} launches per step)",
                   "e2e": "the same plus per-step pinned host->device copies of X, Q and the lengths and the output back",
                   "hbm": f"KV pool resident in HBM; {args.steps} steps per CUDA graph, {n_rep} replays timed one by one"},
         "per_rank": {"kv_bytes_per_step": kv_total, "host_kv_gbs": host_rank_gbs, "streaming_kernel_gbs": attn_rank_gbs,

@@ -49,8 +49,36 @@ struct AttnParams {
     int n_new;                     // trailing tokens per request that are NOT read from the pool
     int total_warps;               // gridDim.x * warps per CTA of the partial kernel
     int min_units;                 // fewest (head-slot, tile) units a warp takes (>= 1)
+    int self_scan;                 // 1: batch <= kSelfScanMax and no prep kernel ran - the kernels work out the tile
+                                   // prefix sums from seq_lens themselves (cum_tiles is not read)
     float scale_log2;              // softmax scale * log2(e)
 };
+
+// Tile prefix sums of a small batch without the prep kernel: warp 0 of every CTA scans seq_lens into shared memory.
+// On a short step the prep launch and the dependency on it are a fifth of the step.  Every thread of the CTA calls
+// this before anything else that might return (it holds a CTA barrier).
+constexpr int kSelfScanMax = 32;
+__device__ __forceinline__ const int* tile_prefix(const AttnParams& p, int* s_cum) {
+    if (!p.self_scan) return p.cum_tiles;
+    if (threadIdx.x < 32) {
+        const int b = threadIdx.x;
+        int v = 0;
+        if (b < p.batch) {
+            const int past = p.seq_lens[b] - p.n_new;
+            v = past > 0 ? (past + 15) / 16 : 0;
+        }
+        int x = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, x, o);
+            if (b >= o) x += y;
+        }
+        s_cum[b + 1] = x;
+        if (b == 0) s_cum[0] = 0;
+    }
+    __syncthreads();
+    return s_cum;
+}
 
 // Units per warp of the streaming grid.  A short step (one 4K request: 2048 units for 2368 warps) would give every
 // warp a single tile and the merge one record per tile; with a floor the work goes to fewer warps, which are taken
@@ -165,16 +193,17 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const PrepParams pp) {
 // Cursor over the linear tile sequence: (request b, head-slot hs = h * nsub + sub, tile).
 // ---------------------------------------------------------------------------
 struct TileCursor {
+    const int* cum;               // [B + 1] exclusive prefix sum of past tiles (global memory, or the CTA's own scan)
     int b, hs, tile, tiles_b;
     __device__ __forceinline__ void locate(const AttnParams& p, long long u, int nhs) {
         int lo = 0, hi = p.batch - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if (static_cast<long long>(p.cum_tiles[mid]) * nhs <= u) lo = mid; else hi = mid - 1;
+            if (static_cast<long long>(cum[mid]) * nhs <= u) lo = mid; else hi = mid - 1;
         }
         b = lo;
-        tiles_b = p.cum_tiles[b + 1] - p.cum_tiles[b];
-        const long long r = u - static_cast<long long>(p.cum_tiles[b]) * nhs;
+        tiles_b = cum[b + 1] - cum[b];
+        const long long r = u - static_cast<long long>(cum[b]) * nhs;
         hs = tiles_b > 0 ? static_cast<int>(r / tiles_b) : 0;
         tile = tiles_b > 0 ? static_cast<int>(r % tiles_b) : 0;
     }
@@ -185,7 +214,7 @@ struct TileCursor {
         hs = 0;
         do {
             ++b;
-            tiles_b = b < p.batch ? p.cum_tiles[b + 1] - p.cum_tiles[b] : 1;
+            tiles_b = b < p.batch ? cum[b + 1] - cum[b] : 1;
         } while (b < p.batch && tiles_b == 0);
     }
 };
@@ -263,8 +292,10 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g4 = lane >> 3, j = lane & 7;
 
+    __shared__ int s_cum[kSelfScanMax + 1];
+    const int* cum = tile_prefix(p, s_cum);
     const int nhs = p.nh_kv * p.nsub;
-    const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
+    const long long U = static_cast<long long>(cum[p.batch]) * nhs;
     const WarpSplit ws = warp_split(p, U);
     const long long qn = ws.qn;
     const int gw = logical_warp(ws, blockIdx.x, warp, NWARPS, gridDim.x);
@@ -285,11 +316,13 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_consta
     __syncwarp();
 
     TileCursor cc, pc;
+    cc.cum = cum;
     cc.locate(p, u0, nhs);
     // Prologue: lane s starts the copies of stage s, so the page-table reads of all stages of the ring are one
     // round trip instead of a chain of them.
     if (lane < depth && u0 + lane < u1) {
         TileCursor c;
+        c.cum = cum;
         c.locate(p, u0 + lane, nhs);
         issue_tile(p, &tmK, &tmV, c, wbase + lane * kStageBytes, &bars[lane]);
     }
@@ -508,6 +541,8 @@ __global__ void __launch_bounds__(merge_threads(WPR)) attn_merge_kernel(const Me
     const AttnParams& p = mp.a;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int part = warp % WPR, row_in_cta = warp / WPR;
+    __shared__ int s_cum[kSelfScanMax + 1];
+    const int* cum = tile_prefix(p, s_cum);
     const long long wid = static_cast<long long>(blockIdx.x) * (kThreads / 32 / WPR) + row_in_cta;
     const bool row_valid = wid < static_cast<long long>(p.batch) * p.nh_q;
     if (WPR == 1 && !row_valid) return;
@@ -520,11 +555,11 @@ __global__ void __launch_bounds__(merge_threads(WPR)) attn_merge_kernel(const Me
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float m = -INFINITY, l = 0.f;
 
-    const int tiles_b = p.cum_tiles[b + 1] - p.cum_tiles[b];
+    const int tiles_b = cum[b + 1] - cum[b];
     if (row_valid && tiles_b > 0) {
-        const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
+        const long long U = static_cast<long long>(cum[p.batch]) * nhs;
         const long long qn = warp_split(p, U).qn;
-        const long long s0 = static_cast<long long>(p.cum_tiles[b]) * nhs + static_cast<long long>(hs) * tiles_b;
+        const long long s0 = static_cast<long long>(cum[b]) * nhs + static_cast<long long>(hs) * tiles_b;
         const long long e0 = s0 + tiles_b;
         const int seg = b * nhs + hs;
         const int gw_first = static_cast<int>(s0 / qn), gw_last = static_cast<int>((e0 - 1) / qn);

@@ -96,7 +96,9 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const int G = p.g_total / p.nsub;                 // query rows per record, <= 16
     const bool hi_rows = G > 8;
     const int nhs = p.nh_kv * p.nsub;
-    const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
+    __shared__ int s_cum[kSelfScanMax + 1];
+    const int* cum = tile_prefix(p, s_cum);
+    const long long U = static_cast<long long>(cum[p.batch]) * nhs;
     const WarpSplit ws = warp_split(p, U);
     const long long qn = ws.qn;
     const int gw = logical_warp(ws, blockIdx.x, warp, NWARPS, gridDim.x);
@@ -117,11 +119,13 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     __syncwarp();
 
     TileCursor cc, pc;
+    cc.cum = cum;
     cc.locate(p, u0, nhs);
     // Prologue: lane s starts the copies of stage s, so the page-table reads of all stages of the ring are one
     // round trip instead of a chain of them.
     if (lane < depth && u0 + lane < u1) {
         TileCursor c;
+        c.cum = cum;
         c.locate(p, u0 + lane, nhs);
         issue_tile_sw(p, &tmK, &tmV, c, wbase + lane * kStageBytes, &bars[lane]);
     }
@@ -332,7 +336,9 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 
     const int G = p.g_total / p.nsub;                 // query heads per record, <= 8
     const int nhs = p.nh_kv * p.nsub;
-    const long long U = static_cast<long long>(p.cum_tiles[p.batch]) * nhs;
+    __shared__ int s_cum[kSelfScanMax + 1];
+    const int* cum = tile_prefix(p, s_cum);
+    const long long U = static_cast<long long>(cum[p.batch]) * nhs;
     const WarpSplit ws = warp_split(p, U);
     const long long qn = ws.qn;
     const int gw = logical_warp(ws, blockIdx.x, warp, NWARPS, gridDim.x);
@@ -353,11 +359,13 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     __syncwarp();
 
     TileCursor cc, pc;
+    cc.cum = cum;
     cc.locate(p, u0, nhs);
     // Prologue: lane s starts the copies of stage s, so the page-table reads of all stages of the ring are one
     // round trip instead of a chain of them.
     if (lane < depth && u0 + lane < u1) {
         TileCursor c;
+        c.cum = cum;
         c.locate(p, u0 + lane, nhs);
         issue_tile_sw(p, &tmK, &tmV, c, wbase + lane * kStageBytes, &bars[lane]);
     }

@@ -152,9 +152,11 @@ struct dkv_context {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     int attn_variant = -1;              // -1: chosen per call from the head grouping
     int attn_ctas = 0;
-    int attn_min_units = 8;          // HBM pools: fewest (head-slot, tile) units per warp of the streaming grid
+    int attn_min_units = 5;          // HBM pools: fewest (head-slot, tile) units per warp of the streaming grid (measured:
+                                     // 2..5 within 0.5 us of each other on 4K-16K single requests, 8 about 1 us slower)
     int proj_split_k = 0;
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
+    int attn_self_scan = 1;             // batches of up to 32: no prep launch, the kernels scan the lengths themselves
     int proj_wide = 1;                  // 256-token projection tiles when there are more 128-token tiles than SMs
     int proj_decode = -1;               // swapped-operand projection kernel: -1 when it can run under the streaming kernel; 0 never; 1 whenever T <= 512
     int attn_mma8 = 1;                  // tensor-core form with the query heads on the N side when <= 8 share a KV head (0: 16-row form)
@@ -917,6 +919,8 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "attn_ctas")) {
         DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
         ctx->attn_ctas = value;
+    } else if (!strcmp(key, "attn_self_scan")) {
+        ctx->attn_self_scan = value != 0;
     } else if (!strcmp(key, "proj_wide")) {
         ctx->proj_wide = value != 0;
     } else if (!strcmp(key, "proj_decode")) {
@@ -1063,9 +1067,15 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
         DKV_CUDA(cudaEventRecord(ctx->ev_fork, st));
         DKV_CUDA(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
     }
-    attn_prep_kernel<<<1, 256, 0, st>>>(prep);
-    DKV_CUDA(cudaGetLastError());
-    ctx->launches += 1 + (a->new_mode == DKV_NEW_GIVEN ? 1 : 0);
+    // Small batches need no prep launch: the streaming and merge kernels scan the lengths themselves, and the
+    // projection places its tokens itself.  Caller-given K/V rows still take their slots from the prep kernel.
+    const bool self_scan = ctx->attn_self_scan != 0 && a->batch <= kSelfScanMax && a->new_mode != DKV_NEW_GIVEN;
+    if (!self_scan) {
+        attn_prep_kernel<<<1, 256, 0, st>>>(prep);
+        DKV_CUDA(cudaGetLastError());
+        ctx->launches += 1;
+    }
+    ctx->launches += (a->new_mode == DKV_NEW_GIVEN ? 1 : 0);
     if (a->new_mode == DKV_NEW_PROJECT) {
         const int g_total = a->nh_q / nh_kv;
         bool rows_on_host = L.pool_on_host;              // where the streaming kernel will read from
@@ -1141,6 +1151,7 @@ static int decode_impl(dkv_context* ctx, const dkv_decode_args* a, void* stream,
     ap.rows_per_box = Lsrc->rows_per_box;
     ap.row_stride = Lsrc->d.row_stride;
     ap.n_new = n_new;
+    ap.self_scan = self_scan ? 1 : 0;
     ap.scale_log2 = a->softmax_scale * 1.4426950408889634f;
     MergeParams mp{};
     mp.kv_new = n_new ? kv_new : nullptr;

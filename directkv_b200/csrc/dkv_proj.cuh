@@ -81,7 +81,10 @@ __device__ __forceinline__ long long proj_tok_slot(const ProjParams& p, int tok)
     const int row = d.row_map ? d.row_map[tok] : tok;
     if (d.page_table == nullptr) return static_cast<long long>(row) * d.row_stride + pos;
     const int pg = pos >> d.page_shift;
-    if (pg >= d.pt_stride || row < 0 || (d.pt_rows > 0 && row >= d.pt_rows)) return -1;   // reported by attn_prep_kernel
+    if (pg >= d.pt_stride || row < 0 || (d.pt_rows > 0 && row >= d.pt_rows)) {
+        atomicOr(p.status, kStatusBadPage);           // the token is not stored
+        return -1;
+    }
     return (static_cast<long long>(d.page_table[static_cast<long long>(row) * d.pt_stride + pg]) << d.page_shift) +
            (pos & (d.page_size - 1));
 }

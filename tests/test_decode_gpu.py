@@ -264,6 +264,31 @@ def test_config2_full_size_properties():
     kernel.unregister_layer(62)
 
 
+def test_scratch_growth_is_refused_under_capture_and_allowed_outside():
+    """A call recorded into a CUDA graph may not allocate: when its scratch need exceeds what the context holds, the
+    entry point says so (size it with dkv_context_reserve or an eager call first) instead of calling cudaMalloc under
+    capture; the same call outside capture grows the scratch and works."""
+    shape = _shape(128, 8, 8, rope=False)
+    big = 200000                                    # 200,000 short requests: about 850 MB of partial records
+    pool = torch.zeros(64, 8, 128, dtype=torch.bfloat16, device=DEV)
+    pool[16:32] = 1.0
+    kernel.register_layer(63, pool, pool.clone(), page_size=16)
+    q = torch.ones(big, 8, 128, dtype=torch.bfloat16, device=DEV)
+    lens = torch.full((big,), 5, dtype=torch.int32, device=DEV)
+    table = torch.ones(big, 1, dtype=torch.int32, device=DEV)
+    out = torch.empty_like(q)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with pytest.raises(RuntimeError, match="before capturing"):
+        with torch.cuda.graph(g):
+            kernel.decode(63, q, lens, shape.scale, page_table=table, out=out)
+    torch.cuda.synchronize()
+    kernel.decode(63, q, lens, shape.scale, page_table=table, out=out)          # eager: grows, then runs
+    get_context(0).raise_on_status()
+    assert torch.equal(out.float(), torch.ones_like(out).float()), "attention over five identical rows returns that row"
+    kernel.unregister_layer(63)
+
+
 def test_dma_staged_decode_matches_streaming():
     """Request-pool layout in pinned host memory: the past rows copied to HBM by cudaMemcpyAsync and attended there
     give the same bits as streaming them from the host pool (same 16-token tiles in the same order), and the new
@@ -369,9 +394,39 @@ def test_units_per_warp_floor(nh_q, nh_kv):
             ctx.set("attn_min_units", floor)
             outs.append(_run_decode(_shape(512, nh_q, nh_kv), [700, 33, 1, 2049], 16, cfg_id=55, kv_on_host=False))
     finally:
-        ctx.set("attn_min_units", 8)
+        ctx.set("attn_min_units", 5)
     for o in outs[1:]:
         assert (o.float() - outs[0].float()).abs().max().item() < 1e-2
+
+
+@pytest.mark.parametrize("nh_q,nh_kv,host", [(4, 4, True), (8, 2, False), (16, 1, False), (8, 8, False)])
+def test_small_batches_without_the_prep_launch(nh_q, nh_kv, host):
+    """Batches of up to 32 requests run without attn_prep_kernel: the streaming and merge kernels scan the lengths
+    themselves and the projection places its tokens itself.  Same bits as with the prep launch (knob off), for
+    lengths that include empty pasts, and the same stored rows."""
+    ctx = get_context(0)
+    shape = _shape(256, nh_q, nh_kv)
+    lens = [1, 1500, 37, 800, 2, 4097, 333, 16, 17] + [64] * 23          # 32 requests
+    res = []
+    try:
+        for flag in (1, 0):
+            ctx.set("attn_self_scan", flag)
+            case = workloads.make_decode_case(shape, lens, 16, 43, DEV, kv_on_host=host)
+            k0, v0 = case["k_pool"].cpu().clone(), case["v_pool"].cpu().clone()     # before the step stores into them
+            kernel.register_layer(92, case["k_pool"], case["v_pool"], case["wk"], case["wv"], case["cos_sin"], page_size=16)
+            lse = torch.empty(len(lens), nh_q, dtype=torch.float32, device=DEV)
+            out = kernel.decode(92, case["q"], case["seq_lens"], shape.scale, page_table=case["page_table"], x=case["x"],
+                                lse_out=lse)
+            ctx.raise_on_status()
+            res.append((out.clone(), lse.clone(), case["k_pool"].cpu().clone(), case["v_pool"].cpu().clone()))
+            kernel.unregister_layer(92)
+    finally:
+        ctx.set("attn_self_scan", 1)
+    for a, b in zip(res[0], res[1]):
+        assert torch.equal(a, b)
+    ref = orc.decode_layer(case["x"].cpu(), case["wk"].cpu(), case["wv"].cpu(), case["q"].cpu(), k0, v0,
+                           case["page_table"].cpu(), lens, 16, case["cos_sin"].cpu(), shape.scale)
+    assert_close(res[0][0], ref.view_as(res[0][0]), "O without the prep launch")
 
 
 def test_errors():
