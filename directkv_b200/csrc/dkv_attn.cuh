@@ -556,6 +556,7 @@ __global__ void __launch_bounds__(merge_threads(WPR)) attn_merge_kernel(const Me
     float m = -INFINITY, l = 0.f;
 
     const int tiles_b = cum[b + 1] - cum[b];
+    int n_parts = 1;              // warps of the row that found records to read
     if (row_valid && tiles_b > 0) {
         const long long U = static_cast<long long>(cum[p.batch]) * nhs;
         const long long qn = warp_split(p, U).qn;
@@ -564,6 +565,8 @@ __global__ void __launch_bounds__(merge_threads(WPR)) attn_merge_kernel(const Me
         const int seg = b * nhs + hs;
         const int gw_first = static_cast<int>(s0 / qn), gw_last = static_cast<int>((e0 - 1) / qn);
         const int n = gw_last - gw_first + 1;
+        n_parts = (n + kMergeBlock - 1) / kMergeBlock;
+        n_parts = n_parts > WPR ? WPR : n_parts;
         const float* rec0 = p.partials + static_cast<size_t>(gw_first + seg) * (mp.G * kPartialStride) + g * kPartialStride;
         const size_t rec_stride = static_cast<size_t>(mp.G) * kPartialStride;
         for (int base = part * kMergeBlock; base < n; base += WPR * kMergeBlock) {
@@ -608,8 +611,9 @@ __global__ void __launch_bounds__(merge_threads(WPR)) attn_merge_kernel(const Me
         if (lane == 0) s_ml[warp] = make_float2(m, l);
         __syncthreads();
         if (part != 0 || !row_valid) return;
-#pragma unroll
-        for (int j = 1; j < WPR; ++j) {
+        // Fold only the warps that had records (a short step leaves a few dozen records for a row that 32 warps
+        // were launched for); the order is fixed, so the result does not depend on WPR's choice.
+        for (int j = 1; j < n_parts; ++j) {
             const float2 ml = s_ml[warp + j];
             const float4 oj = s_acc[warp + j][lane];
             const float mn = fmaxf(m, ml.x);
