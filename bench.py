@@ -1089,12 +1089,12 @@ def main():
 # Bytes per launch of the streaming kernel on the 1-GPU workload, from ncu captures of the default variant
 # (attn_partial_kernel<1,16,1>): with the pool in pinned host memory the traffic that matters crosses PCIe
 # (pcie__read_bytes.sum; DRAM sees 0.2-2 MB), with the pool in HBM it is dram__bytes_read.sum + dram__bytes_write.sum.
-HOST_TRAFFIC_BYTES_PER_LAUNCH = 1_071_760_000
+HOST_TRAFFIC_BYTES_PER_LAUNCH = 1_071_759_872
 HOST_TRAFFIC_SOURCE = ("ncu pcie__read_bytes.sum of one launch (payload 977.6 MB + completion headers), "
-                       "`bench.py --only host`, -k regex:attn_partial -c 2, --clock-control none")
-HBM_TRAFFIC_BYTES_PER_LAUNCH = 985_208_320
-HBM_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum (980.18 MB) + dram__bytes_write.sum (5.03 MB) of one launch, "
-                      "`bench.py --only hbm`, -k regex:attn_partial -c 3, --clock-control none")
+                       "`bench.py --steps 3 --warmup 3 --only host`, -k regex:attn_partial -s 3 -c 2, --clock-control none")
+HBM_TRAFFIC_BYTES_PER_LAUNCH = 980_479_744
+HBM_TRAFFIC_SOURCE = ("ncu dram__bytes_read.sum (980.14 MB) + dram__bytes_write.sum (0.34 MB) of one launch, "
+                      "`bench.py --steps 3 --warmup 3 --only hbm`, -k regex:attn_partial -s 15 -c 3, --clock-control none")
 
 if __name__ == "__main__":
     main()

@@ -804,7 +804,12 @@ int launch_attention(dkv_context* ctx, const LayerState& L, AttnParams& ap, bool
     // segments eight warps share a row.
     const long long rows = static_cast<long long>(ap.batch) * ap.nh_q;
     const long long segments = static_cast<long long>(ap.batch) * ap.nh_kv * ap.nsub;
-    if (segments * 64 < ap.total_warps) attn_merge_kernel<32><<<static_cast<int>(rows), merge_threads(32), 0, st>>>(mp);
+    // A row can have at most (tiles of the longest request the addressing allows) / (tiles per warp) + 2 records; the
+    // 32-warp form pays only when there can be more than 64.
+    const long long max_tokens = paged ? static_cast<long long>(ap.pt_stride) * ap.page_size : ap.row_stride;
+    const long long max_records = max_tokens / kTileTokens / ap.min_units + 2;
+    if (segments * 64 < ap.total_warps && max_records > 64)
+        attn_merge_kernel<32><<<static_cast<int>(rows), merge_threads(32), 0, st>>>(mp);
     else if (segments * 8 < ap.total_warps) attn_merge_kernel<8><<<static_cast<int>(rows), kMergeThreads, 0, st>>>(mp);
     else attn_merge_kernel<1><<<static_cast<int>((rows + 7) / 8), kMergeThreads, 0, st>>>(mp);
     DKV_CUDA(cudaGetLastError());
