@@ -58,6 +58,16 @@ struct AttnParams {
 // On a short step the prep launch and the dependency on it are a fifth of the step.  Every thread of the CTA calls
 // this before anything else that might return (it holds a CTA barrier).
 constexpr int kSelfScanMax = 32;
+constexpr int kSelfScanBytes = 256;                             // room for kSelfScanMax + 1 ints
+
+// Dynamic shared memory of the streaming kernels: the stages, one mbarrier per stage, the CTA's own length scan.
+// (No static shared memory there: the dynamic part is 1 KB-aligned, so a static array would cost a whole KB, and
+// the 16-warp kernels share their SM with the decode projection to within a few hundred bytes.)
+template <int NWARPS, int NST>
+__host__ __device__ constexpr size_t attn_dyn_smem_bytes() {
+    return static_cast<size_t>(NWARPS) * NST * kStageBytes + static_cast<size_t>(NWARPS) * NST * 8 + kSelfScanBytes;
+}
+
 __device__ __forceinline__ const int* tile_prefix(const AttnParams& p, int* s_cum) {
     if (!p.self_scan) return p.cum_tiles;
     if (threadIdx.x < 32) {
@@ -284,15 +294,17 @@ __device__ __forceinline__ float2 mul2(const float2 a, const float2 b) {
 // tile and the head-dim slices [8j, 8j+8) and [64+8j, 64+8j+8); a quarter-warp therefore reads
 // 128 contiguous bytes of a row with each 16-byte shared load (no bank conflicts).
 // ---------------------------------------------------------------------------
+// The 16-warp instance shares its SM with the decode projection (128 threads x 96 registers): 512 x 104 + 128 x 96
+// registers fill the file exactly, so it must stay at 104 (dkv_context_set "check_coresidency" verifies it).
 template <int G, int NWARPS, int NST>
-__global__ void __launch_bounds__(NWARPS * 32, 1)
+__global__ void __maxnreg__(NWARPS == 16 ? (G == 1 ? 104 : 128) : NWARPS == 12 ? 168 : 232)
 attn_partial_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                     const AttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g4 = lane >> 3, j = lane & 7;
 
-    __shared__ int s_cum[kSelfScanMax + 1];
+    int* s_cum = reinterpret_cast<int*>(smem + attn_dyn_smem_bytes<NWARPS, NST>() - kSelfScanBytes);
     const int* cum = tile_prefix(p, s_cum);
     const int nhs = p.nh_kv * p.nsub;
     const long long U = static_cast<long long>(cum[p.batch]) * nhs;

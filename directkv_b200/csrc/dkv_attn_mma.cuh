@@ -96,7 +96,7 @@ attn_partial_mma_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_co
     const int G = p.g_total / p.nsub;                 // query rows per record, <= 16
     const bool hi_rows = G > 8;
     const int nhs = p.nh_kv * p.nsub;
-    __shared__ int s_cum[kSelfScanMax + 1];
+    int* s_cum = reinterpret_cast<int*>(smem + attn_dyn_smem_bytes<NWARPS, NST>() - kSelfScanBytes);
     const int* cum = tile_prefix(p, s_cum);
     const long long U = static_cast<long long>(cum[p.batch]) * nhs;
     const WarpSplit ws = warp_split(p, U);
@@ -336,7 +336,7 @@ attn_partial_mma8_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 
     const int G = p.g_total / p.nsub;                 // query heads per record, <= 8
     const int nhs = p.nh_kv * p.nsub;
-    __shared__ int s_cum[kSelfScanMax + 1];
+    int* s_cum = reinterpret_cast<int*>(smem + attn_dyn_smem_bytes<NWARPS, NST>() - kSelfScanBytes);
     const int* cum = tile_prefix(p, s_cum);
     const long long U = static_cast<long long>(cum[p.batch]) * nhs;
     const WarpSplit ws = warp_split(p, U);

@@ -407,7 +407,7 @@ __global__ void __launch_bounds__(256) stream_copy_kernel(uint4* __restrict__ ds
 // ---------------------------------------------------------------------------
 template <int G, int NW, int NST>
 constexpr size_t attn_smem_bytes() {
-    return static_cast<size_t>(NW) * NST * kStageBytes + static_cast<size_t>(NW) * NST * 8;
+    return attn_dyn_smem_bytes<NW, NST>();
 }
 
 template <int G, int NW, int NST>
@@ -924,6 +924,29 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
     } else if (!strcmp(key, "attn_ctas")) {
         DKV_REQUIRE(value >= 0 && value <= 65535, "attn_ctas out of range");
         ctx->attn_ctas = value;
+    } else if (!strcmp(key, "check_coresidency")) {
+        // The decode projection is built to run UNDER the 16-warp streaming kernels (same SMs, same time).  That
+        // holds only while one CTA of each fits an SM's registers and shared memory together; a few registers more
+        // in a streaming kernel silently turn the overlap into a sequence (+10 us on a 170 us step).
+        DKV_CUDA(cudaSetDevice(ctx->device));
+        cudaDeviceProp prop;
+        DKV_CUDA(cudaGetDeviceProperties(&prop, ctx->device));
+        cudaFuncAttributes pa, sa[2];
+        DKV_CUDA(cudaFuncGetAttributes(&pa, proj_rope_decode_kernel));
+        DKV_CUDA(cudaFuncGetAttributes(&sa[0], attn_partial_kernel<1, 16, 1>));
+        DKV_CUDA(cudaFuncGetAttributes(&sa[1], attn_partial_mma8_kernel<16, 1>));
+        const size_t stream_smem = attn_smem_bytes<1, 16, 1>();
+        for (int i = 0; i < 2; ++i) {
+            const long long regs = 512ll * sa[i].numRegs + 128ll * pa.numRegs;
+            const size_t smem = stream_smem + sa[i].sharedSizeBytes + pd_smem_bytes(kPdMaxTokens) + pa.sharedSizeBytes + 2048;   // + 1 KB per CTA that the system reserves
+            if (regs > prop.regsPerMultiprocessor || smem > prop.sharedMemPerMultiprocessor)
+                return fail(DKV_ERR_UNSUPPORTED,
+                            "the %s streaming kernel (%d registers, %zu B) and the decode projection (%d registers, %zu B) do not "
+                            "fit one SM together (%lld of %d registers, %zu of %zu B)", i ? "tensor-core" : "CUDA-core",
+                            sa[i].numRegs, stream_smem + sa[i].sharedSizeBytes, pa.numRegs,
+                            pd_smem_bytes(kPdMaxTokens) + pa.sharedSizeBytes, regs, prop.regsPerMultiprocessor, smem,
+                            static_cast<size_t>(prop.sharedMemPerMultiprocessor));
+        }
     } else if (!strcmp(key, "attn_self_scan")) {
         ctx->attn_self_scan = value != 0;
     } else if (!strcmp(key, "proj_wide")) {

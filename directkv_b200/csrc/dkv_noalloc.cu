@@ -76,7 +76,7 @@ constexpr int kWarpsG4 = 8, kStagesG4 = 3;      // and for 4
 
 template <int G, int NW, int NST>
 constexpr size_t smem_bytes() {
-    return static_cast<size_t>(NW) * NST * kStageBytes + static_cast<size_t>(NW) * NST * 8;
+    return attn_dyn_smem_bytes<NW, NST>();
 }
 
 // Once per device, with that device current: find the array's address on this device and raise

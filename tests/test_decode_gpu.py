@@ -264,6 +264,13 @@ def test_config2_full_size_properties():
     kernel.unregister_layer(62)
 
 
+def test_streaming_and_projection_kernels_fit_one_sm_together():
+    """The decode projection runs under the 16-warp streaming kernels only while one CTA of each fits an SM's
+    registers and shared memory at once (512 x 104 + 128 x 96 registers fill the file exactly); the library checks it
+    from the compiled kernels' own attributes."""
+    get_context(0).set("check_coresidency", 1)
+
+
 def test_scratch_growth_is_refused_under_capture_and_allowed_outside():
     """A call recorded into a CUDA graph may not allocate: when its scratch need exceeds what the context holds, the
     entry point says so (size it with dkv_context_reserve or an eager call first) instead of calling cudaMalloc under
