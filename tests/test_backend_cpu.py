@@ -111,3 +111,37 @@ def test_hooks_capture_hidden_states_by_kwarg_and_positional():
     runner.model.layers[0](hidden_states=x)
     runner.model.layers[1](x)
     assert be._hidden[0] is x and be._hidden[1] is x
+
+
+def test_padded_graph_replays_are_told_from_requests():
+    """Host logic of the replay hook: SGLang pads a replayed batch up to the captured size with the fill length and a
+    stale or zero request index.  Such a tail entry counts as padding when its index repeats an earlier entry, holds
+    no row, or belongs to a request whose previous length was not fill - 1; the pool keeps a spare row for them."""
+    be, _ = _backend("DirectKVSmpV2Backend")
+    be._ensure_pool()
+    assert be._pool.pad_row == be._pool.max_reqs and be._pool.free_rows == be._pool.max_reqs
+    be._sync_rows([1, 2, 6])
+    be._last_len.update({1: 90, 2: 63, 6: 10})
+    fill = be.get_cuda_graph_seq_len_fill_value()
+    assert be._count_real([1, 2, 6], [91, 64, 11]) == 3                 # nothing padded
+    assert be._count_real([1, 2, 6, 0], [91, 64, 11, fill]) == 3        # index 0 holds no row
+    assert be._count_real([1, 6, 2, 2], [91, 11, 64, fill]) == 3        # repeats an earlier entry
+    assert be._count_real([6, 2, 1, 1], [11, 64, fill, fill]) == 2      # request 1 was 90 tokens long, not 63
+    assert be._count_real([1, 6, 2], [91, 11, fill]) == 3               # request 2 was 63 long: really 64 now
+    assert be._count_real([0, 0, 0, 0], [fill] * 4) == 0                # a capture's placeholders
+    rows = {be._pool.row_of(r) for r in (1, 2, 6)}
+    assert be._pool.pad_row not in rows
+
+
+def test_request_pool_spare_rows_never_enter_the_free_list():
+    from directkv_b200 import DirectKVRequestPool
+
+    pool = DirectKVRequestPool(max_reqs=3, max_seqlen=70, num_kv_heads=2, head_dim=128, num_layers=1, spare_rows=1)
+    assert pool.k_pool[0].shape[0] == 4 and pool.pad_row == 3
+    for rid in (10, 11, 12):
+        pool.alloc(rid)
+    assert sorted(pool.row_of(r) for r in (10, 11, 12)) == [0, 1, 2] and pool.free_rows == 0
+    with pytest.raises(RuntimeError, match="Out of rows"):
+        pool.alloc(13)
+    with pytest.raises(ValueError):
+        DirectKVRequestPool(max_reqs=1, max_seqlen=64, num_kv_heads=1, head_dim=128, num_layers=1).pad_row
