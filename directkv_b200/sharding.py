@@ -162,6 +162,52 @@ class PartialExchange:
             self.handle = None
 
 
+class PeerWatch:
+    """Host-side liveness of the ranks of a partitioned group, over a c10d key-value store (``dist.TCPStore``,
+    ``dist.FileStore``, ...).
+
+    The reference is single-GPU and has no failure detection.  Here a rank that leaves (crash, eviction) would
+    otherwise be noticed by its peers only inside their next collective - or, with the fused exchange, as a
+    two-second device-side wait that runs out.  With a watch every rank publishes the step it is about to start
+    (``beat``) and checks, BEFORE it launches, that every peer has published that step too (``require``): a rank
+    that is gone shows up on the host, within ``timeout_s``, while no kernel or collective of the step is in flight.
+    """
+
+    def __init__(self, store, rank: int, world: int, prefix: str = "directkv_b200/alive"):
+        self.store, self.rank, self.world, self.prefix = store, int(rank), int(world), prefix
+
+    def _key(self, rank: int) -> str:
+        return f"{self.prefix}/{rank}"
+
+    def beat(self, step: int) -> None:
+        self.store.set(self._key(self.rank), str(int(step)))
+
+    def _step_of(self, rank: int) -> int:
+        key = self._key(rank)
+        if not self.store.check([key]):
+            return -1
+        return int(self.store.get(key).decode())
+
+    def missing(self, step: int, timeout_s: float = 1.0, poll_s: float = 0.01) -> List[int]:
+        """Ranks that have not announced ``step`` (or a later one) within ``timeout_s``."""
+        import time
+
+        deadline = time.monotonic() + timeout_s
+        pending = [r for r in range(self.world) if r != self.rank]
+        while pending:
+            pending = [r for r in pending if self._step_of(r) < step]
+            if not pending or time.monotonic() >= deadline:
+                break
+            time.sleep(poll_s)
+        return pending
+
+    def require(self, step: int, timeout_s: float = 1.0) -> None:
+        gone = self.missing(step, timeout_s)
+        if gone:
+            raise RuntimeError(f"directkv_b200: rank(s) {gone} did not reach step {step} within {timeout_s:.1f} s; "
+                               "nothing of this step was launched")
+
+
 def sequence_split_decode(
     layer_id: int,
     q: torch.Tensor,                       # [B, NH_q, 128] bf16 CUDA, replicated on every rank

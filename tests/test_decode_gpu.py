@@ -264,6 +264,42 @@ def test_config2_full_size_properties():
     kernel.unregister_layer(62)
 
 
+def test_lengths_and_rows_that_lead_outside_the_page_table_are_reported_not_read():
+    """seq_lens and row_map are device data the host never sees.  A length beyond the table's width, or a row beyond its
+    rows, sets DKV_STATUS_BAD_PAGE (bit 5): the nearest entry is read instead (the request's output is then wrong, by
+    construction), the new token of such a request is not stored, nothing outside the table is touched, and the context
+    stays usable."""
+    ctx = get_context(0)
+    shape = _shape(128, 4, 4, rope=False)
+    lens = [40, 200, 33]
+    case = workloads.make_decode_case(shape, lens, 16, 77, DEV, kv_on_host=False)
+    kernel.register_layer(64, case["k_pool"], case["v_pool"], case["wk"], case["wv"], None, page_size=16)
+    good = kernel.decode(64, case["q"], case["seq_lens"], shape.scale, page_table=case["page_table"], save_kv_cache=False,
+                         x=case["x"]).clone()
+    assert ctx.read_status(clear=True) == 0
+    k_before = case["k_pool"].clone()
+    too_long = case["seq_lens"].clone()
+    too_long[0] = case["page_table"].size(1) * 16 + 7                      # one page more than the table is wide
+    out = kernel.decode(64, case["q"], too_long, shape.scale, page_table=case["page_table"], x=case["x"])
+    st = ctx.read_status(clear=True)
+    assert st & (1 << 5), f"expected the bad-page bit, got {st:#x}"
+    assert torch.equal(out[1:], good[1:]), "the other requests are not affected"
+    rows = torch.tensor([0, 7, 2], dtype=torch.int32, device=DEV)          # row 7 of a three-row table
+    kernel.decode(64, case["q"], case["seq_lens"], shape.scale, page_table=case["page_table"], row_map=rows,
+                  save_kv_cache=False, x=case["x"])
+    st = ctx.read_status(clear=True)
+    assert st & (1 << 5), f"expected the bad-page bit, got {st:#x}"
+    # request 0 of the first bad call was not stored; requests 1 and 2 were
+    changed = (case["k_pool"] != k_before).flatten(1).any(dim=1).nonzero().flatten().tolist()
+    want = sorted(orc.token_slot(case["page_table"][b].tolist(), lens[b] - 1, 16) for b in (1, 2))
+    assert changed == want, (changed, want)
+    again = kernel.decode(64, case["q"], case["seq_lens"], shape.scale, page_table=case["page_table"], save_kv_cache=False,
+                          x=case["x"])
+    ctx.raise_on_status()
+    assert torch.equal(again, good)
+    kernel.unregister_layer(64)
+
+
 def test_streaming_and_projection_kernels_fit_one_sm_together():
     """The decode projection runs under the 16-warp streaming kernels only while one CTA of each fits an SM's
     registers and shared memory at once (512 x 104 + 128 x 96 registers fill the file exactly); the library checks it

@@ -103,3 +103,85 @@ def _gloo_worker(rank, world, port, n_tokens):
 @pytest.mark.parametrize("n_tokens", [1000, 17])
 def test_sequence_split_and_head_shard_over_gloo(n_tokens):
     mp.spawn(_gloo_worker, args=(2, _free_port(), n_tokens), nprocs=2, join=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Failure detection, made on the host: a rank leaves BETWEEN steps (none of its collectives in flight).
+# ---------------------------------------------------------------------------------------------------
+def _leaving_worker(rank, world, port, store_port, results):
+    from datetime import timedelta
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=timedelta(seconds=5))
+    store = dist.TCPStore("127.0.0.1", store_port, world, is_master=(rank == 0), timeout=timedelta(seconds=10))
+    watch = sharding.PeerWatch(store, rank, world)
+    part = torch.full((8, sharding.PARTIAL_STRIDE), float(rank))
+    # step 0: everybody is there
+    watch.beat(0)
+    watch.require(0, timeout_s=5.0)
+    allp = sharding.all_gather_partials(part)
+    assert allp.shape[0] == world
+    dist.barrier()
+    if rank == 1:
+        results.put((rank, "left after step 0"))
+        os._exit(0)                                  # gone between steps; no collective of its own is pending
+    # step 1: the watch reports the missing rank before anything is launched ...
+    watch.beat(1)
+    try:
+        watch.require(1, timeout_s=0.5)
+        results.put((rank, "watch saw nothing"))
+    except RuntimeError as e:
+        results.put((rank, "watch: " + str(e)))
+    # ... and a rank that goes ahead anyway gets an error from the collective (short process-group timeout), not a hang
+    try:
+        sharding.all_gather_partials(part)
+        results.put((rank, "collective returned"))
+    except Exception as e:                            # gloo: connection closed by peer / timeout
+        results.put((rank, "collective: " + type(e).__name__))
+    os._exit(0)                                      # the group is broken: leave without the usual teardown
+
+
+def test_a_rank_that_leaves_between_steps_is_noticed_on_the_host():
+    ctx = mp.get_context("spawn")
+    results = ctx.SimpleQueue()
+    port, store_port = _free_port(), _free_port()
+    procs = [ctx.Process(target=_leaving_worker, args=(r, 2, port, store_port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive(), "a rank hung"
+    got = {}
+    while not results.empty():
+        rank, msg = results.get()
+        got.setdefault(rank, []).append(msg)
+    assert got[1] == ["left after step 0"]
+    assert any(m.startswith("watch: ") and "rank(s) [1]" in m and "step 1" in m for m in got[0]), got
+    assert any(m.startswith("collective: ") for m in got[0]), got
+
+
+def test_peer_watch_with_a_plain_store():
+    """PeerWatch logic against an in-memory stand-in of the c10d store interface."""
+    class Store:
+        def __init__(self):
+            self.d = {}
+
+        def set(self, k, v):
+            self.d[k] = v.encode() if isinstance(v, str) else v
+
+        def get(self, k):
+            return self.d[k]
+
+        def check(self, keys):
+            return all(k in self.d for k in keys)
+
+    st = Store()
+    w0, w1, w2 = (sharding.PeerWatch(st, r, 3) for r in range(3))
+    w0.beat(4)
+    w1.beat(4)
+    assert w0.missing(4, timeout_s=0.05) == [2]
+    w2.beat(5)                                       # a peer that is already a step ahead counts as present
+    assert w0.missing(4, timeout_s=0.05) == []
+    with pytest.raises(RuntimeError, match=r"rank\(s\) \[0, 1\] did not reach step 5"):
+        w2.require(5, timeout_s=0.05)
