@@ -25,6 +25,8 @@
 // TMEM columns: S_0 [0,64) [64,128)   S_1 [128,192) [192,256)   O_0 [256,384)   O_1 [384,512).
 #pragma once
 
+#include <type_traits>
+
 #include "dkv_extend.cuh"
 
 
@@ -33,7 +35,9 @@ namespace dkv {
 constexpr int kPpSlots = 5;                                   // ring of [128 x 128] bf16 tiles: K and V alternate
 constexpr int kPpThreads = 416;                               // 13 warps: producer, 4 issuers, 2 x 4 softmax
 constexpr int kPpSmem = 2 * kExtTileBytes /*Q0,Q1*/ + kPpSlots * kExtTileBytes + 256 + 1024;
-constexpr float kPpRescaleStep = 8.f;                         // log2 units the maximum may lag behind
+constexpr float kPpRescaleStep = 8.f;                         // log2 units the maximum may lag behind where it is taken
+constexpr float kPpOverflowLog2 = 40.f;                       // a probability above 2^40 sends a half-tile back for its maximum
+constexpr float kPpOverflowSum = 1099511627776.f;             // 2^40: the same test on the row sum of a half-tile
 constexpr int kPpHalf = 64;                                   // keys per half-tile
 constexpr int kPpPolyMask = 6;                 // pairs i with (i & mask) == mask go to the FMA pipe: 6 = every fourth (measured best), 2 = every second, 0x40 = none
 
@@ -245,101 +249,129 @@ extend_attn_pp_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
             const uint32_t tSb = tS + bf * kPpHalf;
             // Warp-uniform: only half-tiles on the diagonal (or holding the end of the request) need the comparison.
             const bool masked = (col0 + kPpHalf - 1 > first_limit) || !(p.scale_log2 > 0.f);
-            uint32_t r0[32], r1[32];                          // the row's 64 scores stay in registers
-            tmem_ld_32x32(tSb, r0);
-            tmem_ld_32x32(tSb + 32, r1);
-            tmem_ld_wait();
-            float m_tile = -INFINITY;
-            if (masked) {
+            uint32_t r0[32], r1[32], pk[32];                  // the row's 64 scores stay in registers
+            float psum;
+            // Most half-tiles take no row maximum at all: probabilities are formed against the reference the row
+            // already has, and only if one of them would come out above 2^kPpOverflowLog2 (seen in the sum, and for
+            // the pairs on the FMA pipe in their arguments) is the half-tile done again with its maximum taken and
+            // the reference moved.  Floating point keeps the relative precision of P, l and O whatever the offset.
+            // Returns whether the half-tile has to be done again with its maximum taken (never when it was).
+            auto sweep = [&](auto with_max_tag) -> bool {
+                constexpr bool with_max = decltype(with_max_tag)::value;
+                tmem_ld_32x32(tSb, r0);
+                tmem_ld_32x32(tSb + 32, r1);
+                tmem_ld_wait();
+                if constexpr (with_max) {
+                    float m_tile = -INFINITY;
+                    if (masked) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    if (col0 + i <= my_limit) m_tile = fmaxf(m_tile, __uint_as_float(r0[i]) * p.scale_log2);
-                    if (col0 + 32 + i <= my_limit) m_tile = fmaxf(m_tile, __uint_as_float(r1[i]) * p.scale_log2);
-                }
-            } else {
-                float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;     // four short chains
+                        for (int i = 0; i < 32; ++i) {
+                            if (col0 + i <= my_limit) m_tile = fmaxf(m_tile, __uint_as_float(r0[i]) * p.scale_log2);
+                            if (col0 + 32 + i <= my_limit) m_tile = fmaxf(m_tile, __uint_as_float(r1[i]) * p.scale_log2);
+                        }
+                    } else {
+                        float a0 = -INFINITY, a1 = -INFINITY, a2 = -INFINITY, a3 = -INFINITY;     // four short chains
 #pragma unroll
-                for (int i = 0; i < 16; i += 2) {
-                    a0 = fmax3(a0, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
-                    a1 = fmax3(a1, __uint_as_float(r0[16 + i]), __uint_as_float(r0[17 + i]));
-                    a2 = fmax3(a2, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
-                    a3 = fmax3(a3, __uint_as_float(r1[16 + i]), __uint_as_float(r1[17 + i]));
-                }
-                a0 = fmaxf(a0, a2);
-                a1 = fmaxf(a1, a3);
-                m_tile = fmaxf(a0, a1) * p.scale_log2;            // scale_log2 > 0 on this path
-            }
-            // Move the reference maximum only when the true one is more than the step above it (warp-uniform):
-            // then O and l are rescaled; otherwise probabilities are formed against the old reference (<= 2^8).
-            const bool grow = (m_tile > m_used + kPpRescaleStep) || (m_used == -INFINITY);
-            const bool any_grow = __any_sync(0xffffffffu, grow);
-            if (any_grow) {
-                float m_to = fmaxf(m_used, m_tile);
-                if (m_to == -INFINITY) m_to = 0.f;
-                const float alpha = exp2f(m_used - m_to);             // 0 on the first half-tile
-                l *= alpha;
-                m_used = m_to;
-                if (t > 0) {
-                    // O must be at rest: P V(t - 1) is the last product issued for this tile.
-                    ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_o[g][(t - 1) & 1], ((t - 1) >> 1) & 1) && !ctl->abort);
-                    if (!ok) break;
-                    tc_fence_after_sync();
-#pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t r[32];
-                        tmem_ld_32x32(tO + c * 32, r);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st_32x32(tO + c * 32, r);
+                        for (int i = 0; i < 16; i += 2) {
+                            a0 = fmax3(a0, __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
+                            a1 = fmax3(a1, __uint_as_float(r0[16 + i]), __uint_as_float(r0[17 + i]));
+                            a2 = fmax3(a2, __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
+                            a3 = fmax3(a3, __uint_as_float(r1[16 + i]), __uint_as_float(r1[17 + i]));
+                        }
+                        a0 = fmaxf(a0, a2);
+                        a1 = fmaxf(a1, a3);
+                        m_tile = fmaxf(a0, a1) * p.scale_log2;            // scale_log2 > 0 on this path
                     }
-                    tmem_st_wait();
+                    // Move the reference only when the true maximum is more than the step above it (warp-uniform):
+                    // then O and l are rescaled; otherwise probabilities are formed against the old reference.
+                    const bool grow = (m_tile > m_used + kPpRescaleStep) || (m_used == -INFINITY);
+                    if (__any_sync(0xffffffffu, grow)) {
+                        float m_to = fmaxf(m_used, m_tile);
+                        if (m_to == -INFINITY) m_to = 0.f;
+                        const float alpha = exp2f(m_used - m_to);             // 0 on the first half-tile
+                        l *= alpha;
+                        m_used = m_to;
+                        if (t > 0) {
+                            // O must be at rest: P V(t - 1) is the last product issued for this tile.
+                            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&ctl->bar_o[g][(t - 1) & 1], ((t - 1) >> 1) & 1) && !ctl->abort);
+                            if (!ok) return false;
+                            tc_fence_after_sync();
+#pragma unroll 1
+                            for (int c = 0; c < 4; ++c) {
+                                uint32_t r[32];
+                                tmem_ld_32x32(tO + c * 32, r);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                                tmem_st_32x32(tO + c * 32, r);
+                            }
+                            tmem_st_wait();
+                        }
+                    }
                 }
-            }
-            // Probabilities, packed two bf16 per 32-bit column, go back into the first 32 columns of the S buffer.
-            const float neg_m = -m_used;
-            uint32_t pk[32];
-            // In place and in phases (scale and shift, exponentials, mask, sums and packing), so that each phase is a
-            // run of independent instructions on one pipe.
-            const uint64_t sc2 = f32x2(p.scale_log2, p.scale_log2), nm2 = f32x2(neg_m, neg_m);
-            float* x0 = reinterpret_cast<float*>(r0);
-            float* x1 = reinterpret_cast<float*>(r1);
+                // Probabilities, packed two bf16 per 32-bit column, go back into the first 32 columns of the S buffer.
+                // In place and in phases (scale and shift, exponentials, mask, sums and packing), so that each phase is
+                // a run of independent instructions on one pipe.
+                const float neg_m = -m_used;
+                const uint64_t sc2 = f32x2(p.scale_log2, p.scale_log2), nm2 = f32x2(neg_m, neg_m);
+                float* x0 = reinterpret_cast<float*>(r0);
+                float* x1 = reinterpret_cast<float*>(r1);
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                f32x2_split(fma_f32x2(f32x2(x0[i], x0[i + 1]), sc2, nm2), x0[i], x0[i + 1]);
-                f32x2_split(fma_f32x2(f32x2(x1[i], x1[i + 1]), sc2, nm2), x1[i], x1[i + 1]);
-            }
-#pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                if ((i & kPpPolyMask) == kPpPolyMask) {       // this pair on the FMA pipe
-                    f32x2_split(ex2_poly_f32x2(f32x2(x0[i], x0[i + 1])), x0[i], x0[i + 1]);
-                    f32x2_split(ex2_poly_f32x2(f32x2(x1[i], x1[i + 1])), x1[i], x1[i + 1]);
-                } else {
-                    x0[i] = ex2_approx(x0[i]);
-                    x0[i + 1] = ex2_approx(x0[i + 1]);
-                    x1[i] = ex2_approx(x1[i]);
-                    x1[i + 1] = ex2_approx(x1[i + 1]);
+                for (int i = 0; i < 32; i += 2) {
+                    f32x2_split(fma_f32x2(f32x2(x0[i], x0[i + 1]), sc2, nm2), x0[i], x0[i + 1]);
+                    f32x2_split(fma_f32x2(f32x2(x1[i], x1[i + 1]), sc2, nm2), x1[i], x1[i + 1]);
                 }
-            }
-            if (masked) {
+                float big = -INFINITY;                        // largest argument among the pairs of the FMA pipe
+                if constexpr (!with_max) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    if (col0 + i > my_limit) x0[i] = 0.f;
-                    if (col0 + 32 + i > my_limit) x1[i] = 0.f;
+                    for (int i = 0; i < 32; i += 2)
+                        if ((i & kPpPolyMask) == kPpPolyMask) {
+                            big = fmax3(big, x0[i], x0[i + 1]);
+                            big = fmax3(big, x1[i], x1[i + 1]);
+                        }
                 }
-            }
-            uint64_t sa = f32x2(0.f, 0.f), sb = sa;
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-                sa = add_f32x2(sa, f32x2(x0[i], x0[i + 1]));
-                sb = add_f32x2(sb, f32x2(x1[i], x1[i + 1]));
-                pk[i >> 1] = pack_bf16x2(x0[i], x0[i + 1]);
-                pk[16 + (i >> 1)] = pack_bf16x2(x1[i], x1[i + 1]);
+                for (int i = 0; i < 32; i += 2) {
+                    if ((i & kPpPolyMask) == kPpPolyMask) {       // this pair on the FMA pipe
+                        f32x2_split(ex2_poly_f32x2(f32x2(x0[i], x0[i + 1])), x0[i], x0[i + 1]);
+                        f32x2_split(ex2_poly_f32x2(f32x2(x1[i], x1[i + 1])), x1[i], x1[i + 1]);
+                    } else {
+                        x0[i] = ex2_approx(x0[i]);
+                        x0[i + 1] = ex2_approx(x0[i + 1]);
+                        x1[i] = ex2_approx(x1[i]);
+                        x1[i + 1] = ex2_approx(x1[i + 1]);
+                    }
+                }
+                if (masked) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        if (col0 + i > my_limit) x0[i] = 0.f;
+                        if (col0 + 32 + i > my_limit) x1[i] = 0.f;
+                    }
+                }
+                uint64_t sa = f32x2(0.f, 0.f), sb = sa;
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    sa = add_f32x2(sa, f32x2(x0[i], x0[i + 1]));
+                    sb = add_f32x2(sb, f32x2(x1[i], x1[i + 1]));
+                    pk[i >> 1] = pack_bf16x2(x0[i], x0[i + 1]);
+                    pk[16 + (i >> 1)] = pack_bf16x2(x1[i], x1[i + 1]);
+                }
+                float s4[4];
+                f32x2_split(sa, s4[0], s4[1]);
+                f32x2_split(sb, s4[2], s4[3]);
+                psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+                if constexpr (with_max) return false;
+                // NaN and infinity fail the first comparison too.
+                const bool over = !(psum < kPpOverflowSum) || big > kPpOverflowLog2;
+                return __any_sync(0xffffffffu, over);
+            };
+            if ((t == 0) || masked) {
+                sweep(std::true_type{});
+            } else if (sweep(std::false_type{})) {
+                sweep(std::true_type{});                      // S(t) is still in tensor memory: once more, with its maximum
             }
-            float s4[4];
-            f32x2_split(sa, s4[0], s4[1]);
-            f32x2_split(sb, s4[2], s4[3]);
-            const float psum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+            if (!ok) break;
             tmem_st_32x32(tSb, pk);
             tmem_st_wait();
             l += psum;

@@ -207,6 +207,32 @@ def test_extend_large_scores_rescale():
     _run_fwd(X, Wk, Wv, Q, K, V, cs, True, S_past, kv_on_host=False)
 
 
+@pytest.mark.parametrize("spike", [60.0, 400.0, 3000.0])
+def test_extend_scores_that_outgrow_the_row_reference(spike):
+    """Half-tiles off the diagonal form their probabilities against the reference maximum the row already has and take
+    no maximum of their own; a key whose score lies far above everything before it (2^60 ... beyond what exp2 can
+    hold) sends that half-tile back for its maximum.  Spikes at several places of the past, one in the first
+    half-tile, one right before the diagonal, and rows that never see one."""
+    nh_q, nh_kv, S_new, S_past = 8, 2, 300, 1500
+    total = S_past + S_new
+    g = torch.Generator().manual_seed(77)
+    Q = torch.randn(1, S_new, nh_q, 128, generator=g).to(torch.bfloat16)
+    K = (torch.randn(1, total, nh_kv, 128, generator=g) * 0.5).to(torch.bfloat16)
+    V = torch.randn(1, total, nh_kv, 128, generator=g).to(torch.bfloat16)
+    # a key parallel to one query scores |q|^2 * c * scale with that query and something random with the others
+    for key, qrow, head in ((5, 10, 0), (700, 10, 0), (701, 40, 3), (1290, 250, 5), (1499, 299, 7), (1600, 120, 1)):
+        q = Q[0, qrow, head].float()
+        c = spike / (float(q @ q) * SCALE * 1.4426950408889634)
+        K[0, key, head // (nh_q // nh_kv)] = (q * c).to(torch.bfloat16)
+    kernel.register_layer(73, K.to(DEV), V.to(DEV), row_stride=total)
+    out = kernel.extend_attend(73, Q.to(DEV), SCALE, True, S_past)
+    get_context(0).raise_on_status()
+    ref = orc.sdpa_extend(Q[0], K[0], V[0], S_past, SCALE)
+    assert torch.isfinite(out.float()).all()
+    assert_close(out[0], ref, f"spike {spike}")
+    kernel.unregister_layer(73)
+
+
 @pytest.mark.parametrize("page_size,host", [(1, True), (1, False), (16, True), (64, False)])
 @pytest.mark.parametrize("S_new,S_past", [(200, 0), (130, 333)])
 def test_extend_attend_paged_pool(page_size, host, S_new, S_past):
