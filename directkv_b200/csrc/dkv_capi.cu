@@ -17,6 +17,7 @@
 #include "dkv_attn.cuh"
 #include "dkv_attn_mma.cuh"
 #include "dkv_proj_decode.cuh"
+#include "dkv_proj_gemv.cuh"
 #include "dkv_extend_pp.cuh"
 #include "dkv_extend.cuh"
 #include "dkv_proj.cuh"
@@ -158,6 +159,7 @@ struct dkv_context {
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
     int attn_self_scan = 1;             // batches of up to 32: no prep launch, the kernels scan the lengths themselves
     int proj_wide = 1;                  // 256-token projection tiles when there are more 128-token tiles than SMs
+    int proj_gemv = 1;                  // one or two tokens into a device pool: matrix-vector kernel on the CUDA cores
     int proj_decode = -1;               // swapped-operand projection kernel: -1 when it can run under the streaming kernel; 0 never; 1 whenever T <= 512
     int attn_mma8 = 1;                  // tensor-core form with the query heads on the N side when <= 8 share a KV head (0: 16-row form)
     int attn_mma = -1;                  // -1: tensor-core inner product when 2..16 query heads share a KV head of an HBM pool; 0 never; 1 always
@@ -474,6 +476,12 @@ cudaError_t prefer_max_shared(K kernel) {
     return cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
 }
 
+template <int T>
+cudaError_t set_gemv_attributes() {
+    cudaError_t e = cudaFuncSetAttribute(proj_rope_gemv_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGvSmemBudget);
+    return e != cudaSuccess ? e : prefer_max_shared(proj_rope_gemv_kernel<T>);
+}
+
 template <int NW, int NST>
 cudaError_t attn_mma8_set_attr() {
     cudaError_t e = cudaFuncSetAttribute(attn_partial_mma8_kernel<NW, NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -722,6 +730,9 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
     // The swapped-operand kernel pays off where it runs UNDER the streaming kernel (the 16-warp CUDA-core form
     // leaves it registers and shared memory); alone, the 128-token-tile kernel with its deeper ring is faster.
     const bool small = T <= kPdMaxBatch && (ctx->proj_decode == 1 || (ctx->proj_decode < 0 && beside_streaming));
+    // One or two tokens into a pool in device memory: a matrix-vector stream on the CUDA cores (two-byte stores
+    // per dimension pair are fine for HBM, not for rows behind the host link).
+    const bool tiny = ctx->proj_gemv != 0 && gv_supports(T, L.d.hidden) && k_dst == nullptr && !(store_pool && L.pool_on_host);
     ProjParams pp{};
     pp.T = T;
     pp.H = L.d.hidden;
@@ -749,7 +760,16 @@ int launch_projection(dkv_context* ctx, const LayerState& L, const void* x, int 
     pp.splitk_scratch = splitk;
     pp.tile_counters = ctx->counters;
     pp.status = ctx->status;
-    if (small) {
+    if (tiny) {
+        const int ctas = (L.d.nh_kv * 128 + kGvWarps - 1) / kGvWarps;      // a warp per row pair at most
+        const int grid = ctas < ctx->sm_count ? ctas : ctx->sm_count;
+        const size_t smem = gv_smem_bytes(T, L.d.hidden);
+        const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+        const __nv_bfloat16* wkb = static_cast<const __nv_bfloat16*>(L.d.wk);
+        const __nv_bfloat16* wvb = static_cast<const __nv_bfloat16*>(L.d.wv);
+        if (T == 1) proj_rope_gemv_kernel<1><<<grid, 128, smem, st>>>(xb, wkb, wvb, pp);
+        else proj_rope_gemv_kernel<2><<<grid, 128, smem, st>>>(xb, wkb, wvb, pp);
+    } else if (small) {
         dim3 grid(L.d.nh_kv, pp.split_k, (T + kPdMaxTokens - 1) / kPdMaxTokens);
         proj_rope_decode_kernel<<<grid, 128, pd_smem_bytes(pd_box_rows), st>>>(tmX, L.tmWk, L.tmWv, pp);
     } else if (wide) {
@@ -876,6 +896,8 @@ int dkv_context_create(int device, dkv_context** out) {
         e = cudaFuncSetAttribute(proj_rope_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(pd_smem_bytes(kPdMaxTokens)));
     if (e == cudaSuccess) e = prefer_max_shared(proj_rope_decode_kernel);
+    if (e == cudaSuccess) e = set_gemv_attributes<1>();
+    if (e == cudaSuccess) e = set_gemv_attributes<2>();
     if (e == cudaSuccess) e = prefer_max_shared(attn_partial_kernel<1, 16, 1>);
     if (e != cudaSuccess) {
         delete ctx;
@@ -947,10 +969,23 @@ int dkv_context_set(dkv_context* ctx, const char* key, int value) {
                             pd_smem_bytes(kPdMaxTokens) + pa.sharedSizeBytes, regs, prop.regsPerMultiprocessor, smem,
                             static_cast<size_t>(prop.sharedMemPerMultiprocessor));
         }
+        cudaFuncAttributes ga;
+        DKV_CUDA(cudaFuncGetAttributes(&ga, proj_rope_gemv_kernel<kGvMaxTokens>));
+        for (int i = 0; i < 2; ++i) {
+            const long long regs = 512ll * sa[i].numRegs + 128ll * ga.numRegs;
+            const size_t smem = stream_smem + sa[i].sharedSizeBytes + kGvSmemBudget + ga.sharedSizeBytes + 2048;
+            if (regs > prop.regsPerMultiprocessor || smem > prop.sharedMemPerMultiprocessor)
+                return fail(DKV_ERR_UNSUPPORTED,
+                            "the %s streaming kernel and the matrix-vector projection do not fit one SM together "
+                            "(%lld of %d registers, %zu of %zu B)", i ? "tensor-core" : "CUDA-core", regs,
+                            prop.regsPerMultiprocessor, smem, static_cast<size_t>(prop.sharedMemPerMultiprocessor));
+        }
     } else if (!strcmp(key, "attn_self_scan")) {
         ctx->attn_self_scan = value != 0;
     } else if (!strcmp(key, "proj_wide")) {
         ctx->proj_wide = value != 0;
+    } else if (!strcmp(key, "proj_gemv")) {
+        ctx->proj_gemv = value != 0;
     } else if (!strcmp(key, "proj_decode")) {
         DKV_REQUIRE(value >= -1 && value <= 1, "proj_decode must be -1, 0 or 1");
         ctx->proj_decode = value;

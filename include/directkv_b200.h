@@ -77,7 +77,8 @@ int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv,
  * side of the tensor-core product when at most 8 share a KV head, default; 0 = always the 16-row form), "extend_rowwise" (0/1),
  * "extend_pingpong" (1 = two query tiles per CTA, default; 0 = first form of the extend kernel), "proj_decode"
  * (-1 = use the decode-batch projection kernel where it can run under the streaming kernel, 0 = never, 1 = for
- * every batch of up to 512 tokens), "proj_wide" (0 = 128-token projection tiles only), "attn_ctas" (CTAs of the streaming kernel,
+ * every batch of up to 512 tokens), "proj_gemv" (1 = one or two new tokens going to a pool in device memory are projected by the
+ * matrix-vector kernel on the CUDA cores, default; 0 = always a tensor-core kernel), "proj_wide" (0 = 128-token projection tiles only), "attn_ctas" (CTAs of the streaming kernel,
  * 0 = one per SM), "attn_min_units" (pools in device memory: fewest 16-token tiles a warp of the streaming kernel takes, so
  * that short steps leave few partial records to merge; 1..64, default 5), "check_coresidency" (any value: verifies that a 16-warp streaming CTA and a decode-projection
  * CTA fit one SM together, DKV_ERR_UNSUPPORTED with the register and shared-memory figures otherwise), "attn_self_scan" (1 = batches of up to 32 requests run without the

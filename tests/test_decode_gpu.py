@@ -300,6 +300,27 @@ def test_lengths_and_rows_that_lead_outside_the_page_table_are_reported_not_read
     kernel.unregister_layer(64)
 
 
+@pytest.mark.parametrize("shape,lens", [(workloads.LLAMA3_8B, [300]), (workloads.LLAMA3_8B, [77, 1041]),
+                                        (workloads.OPT_6_7B, [513]), (_shape(7168, 14, 7), [40, 2]),
+                                        (_shape(1024, 4, 4, rope=False), [1, 130])])
+def test_matrix_vector_projection_against_the_oracle_and_the_tensor_core_kernel(shape, lens):
+    """One or two new tokens into a pool in HBM are projected by the matrix-vector kernel (proj_gemv = 1, default),
+    larger batches and host pools by a tensor-core kernel.  Both forms: outputs, the stored K/V rows and the untouched
+    slots against the oracle; the outputs of the two forms agree within the tolerance (the fp32 sums run in another
+    order); each form gives the same bits when the same step runs twice."""
+    ctx = get_context(0)
+    outs = {}
+    for gemv in (1, 0):
+        ctx.set("proj_gemv", gemv)
+        try:
+            outs[gemv] = _run_decode(shape, lens, 16, cfg_id=5, kv_on_host=False, lid=66).clone()
+            again = _run_decode(shape, lens, 16, cfg_id=5, kv_on_host=False, lid=66)
+        finally:
+            ctx.set("proj_gemv", 1)
+        assert torch.equal(outs[gemv], again), f"gemv={gemv}: two runs of the same step differ"
+    assert_close(outs[1], outs[0].float(), "matrix-vector against tensor-core projection")
+
+
 def test_streaming_and_projection_kernels_fit_one_sm_together():
     """The decode projection runs under the 16-warp streaming kernels only while one CTA of each fits an SM's
     registers and shared memory at once (512 x 104 + 128 x 96 registers fill the file exactly); the library checks it
