@@ -9,7 +9,10 @@ ones are those that span many warps and many partial records.  Workloads:
   * Llama-3-8B layer, 64 requests with lognormal context (median 8K, clipped to [256, 128K]), three steps with
     10 % of the requests replaced before each later step (pool in HBM);
   * OPT-30B layer shard, 7 of 56 heads, hidden 7168, 32 requests of 16K (pool in HBM);
-  * Llama-3-8B layer, one request of 32K and one of 128K tokens streamed from a pool in pinned HOST memory.
+  * Llama-3-8B layer, one request of 32K and one of 128K tokens streamed from a pool in pinned HOST memory;
+  * the single-request steps of the short-step probes with the pool in HBM (Llama-3-8B 4K and 128K, OPT-6.7B 4K, two
+    Llama requests): one or two new tokens go through the matrix-vector projection, a 128K request through the widest
+    merge.
 """
 
 import pytest
@@ -82,3 +85,9 @@ def test_opt30b_shard_full_size():
 @pytest.mark.parametrize("ctx_len", [32768, 131072])
 def test_llama3_long_request_from_a_host_pool(ctx_len):
     _check_full_batch(workloads.LLAMA3_8B, [ctx_len + 1], 2, True, 73, f"llama3-8b one request of {ctx_len} from host memory")
+
+
+@pytest.mark.parametrize("shape,lens", [(workloads.LLAMA3_8B, [4097]), (workloads.LLAMA3_8B, [131073]),
+                                        (workloads.OPT_6_7B, [4097]), (workloads.LLAMA3_8B, [16385, 4097])])
+def test_single_request_steps_with_the_pool_in_hbm(shape, lens):
+    _check_full_batch(shape, lens, 6, False, 74, f"{shape.name} short step {lens}")
