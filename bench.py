@@ -340,6 +340,7 @@ def measure_request_pool(dev, lens, steps=5, warmup=2):
 
 
 SHORT_CASES = {
+    "llama1k": ("llama3-8b layer, one request of 1024 stored tokens", workloads.LLAMA3_8B, [1025]),
     "llama4k": ("llama3-8b layer, one request of 4096 stored tokens", workloads.LLAMA3_8B, [4097]),
     "opt4k": ("opt-6.7b layer, one request of 4096 stored tokens", workloads.OPT_6_7B, [4097]),
     "llama16k": ("llama3-8b layer, one request of 16384 stored tokens", workloads.LLAMA3_8B, [16385]),

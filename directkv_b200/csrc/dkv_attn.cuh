@@ -48,7 +48,7 @@ struct AttnParams {
     long long row_stride;          // contiguous mode: slots per pool row
     int n_new;                     // trailing tokens per request that are NOT read from the pool
     int total_warps;               // gridDim.x * warps per CTA of the partial kernel
-    int min_units;                 // fewest (head-slot, tile) units a warp takes (>= 1)
+    int min_units;                 // fewer (head-slot, tile) units per warp of the grid than this: a short step (warp_split)
     int self_scan;                 // 1: batch <= kSelfScanMax and no prep kernel ran - the kernels work out the tile
                                    // prefix sums from seq_lens themselves (cum_tiles is not read)
     float scale_log2;              // softmax scale * log2(e)
@@ -91,8 +91,8 @@ __device__ __forceinline__ const int* tile_prefix(const AttnParams& p, int* s_cu
 }
 
 // Units per warp of the streaming grid.  A short step (one 4K request: 2048 units for 2368 warps) would give every
-// warp a single tile and the merge one record per tile; with a floor the work goes to fewer warps, which are taken
-// one per CTA in turn (sm_spread) so that the rows still come through all SMs' load paths.
+// warp a single tile and the merge one record per tile; there the work goes to fewer warps, which are taken
+// one per CTA in turn (spread) so that the rows still come through all SMs' load paths.
 struct WarpSplit {
     long long qn;
     bool spread;
@@ -101,7 +101,14 @@ __device__ __forceinline__ WarpSplit warp_split(const AttnParams& p, long long U
     WarpSplit w;
     w.qn = (U + p.total_warps - 1) / p.total_warps;
     w.spread = w.qn < p.min_units;
-    if (w.spread) w.qn = p.min_units;
+    if (w.spread) {
+        // A short step: fewer than min_units units per warp of the grid.  Measured over one to eight requests of 1K to
+        // 32K tokens, the step is shortest with about eleven of a CTA's sixteen warps at work and at least two units
+        // each (one 4K request of a Llama-3-8B layer: two units 13.2 us, five 14.3; 8192 units: four 30.7, five 29.1).
+        const long long target = static_cast<long long>(p.total_warps) * 45 / 64;
+        w.qn = (U + target - 1) / target;
+        if (w.qn < 2) w.qn = 2;
+    }
     return w;
 }
 // Ring depth of a warp.  Normally every warp owns NST stages.  On a short step (spread mode) only the first few

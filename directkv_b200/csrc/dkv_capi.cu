@@ -153,8 +153,8 @@ struct dkv_context {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     int attn_variant = -1;              // -1: chosen per call from the head grouping
     int attn_ctas = 0;
-    int attn_min_units = 5;          // HBM pools: fewest (head-slot, tile) units per warp of the streaming grid (measured:
-                                     // 2..5 within 0.5 us of each other on 4K-16K single requests, 8 about 1 us slower)
+    int attn_min_units = 5;          // HBM pools: a step with fewer (head-slot, tile) units per warp of the streaming grid than
+                                     // this is split the short-step way (warp_split)
     int proj_split_k = 0;
     int wait_limit_ms = 2000;           // limit of the exchange consumer's wait for its peers
     int attn_self_scan = 1;             // batches of up to 32: no prep launch, the kernels scan the lengths themselves

@@ -79,8 +79,9 @@ int dkv_context_reserve(dkv_context* ctx, int64_t max_rows, int nh_q, int nh_kv,
  * (-1 = use the decode-batch projection kernel where it can run under the streaming kernel, 0 = never, 1 = for
  * every batch of up to 512 tokens), "proj_gemv" (1 = one or two new tokens going to a pool in device memory are projected by the
  * matrix-vector kernel on the CUDA cores, default; 0 = always a tensor-core kernel), "proj_wide" (0 = 128-token projection tiles only), "attn_ctas" (CTAs of the streaming kernel,
- * 0 = one per SM), "attn_min_units" (pools in device memory: fewest 16-token tiles a warp of the streaming kernel takes, so
- * that short steps leave few partial records to merge; 1..64, default 5), "check_coresidency" (any value: verifies that a 16-warp streaming CTA and a decode-projection
+ * 0 = one per SM), "attn_min_units" (pools in device memory: a step with fewer 16-token tiles per warp of the streaming grid than this
+ * is a short step - its tiles go to about 70 % of the warps, two or more per warp, dealt out over the CTAs in turn; 1..64, default 5;
+ * 1 = never), "check_coresidency" (any value: verifies that a 16-warp streaming CTA and a decode-projection
  * CTA fit one SM together, DKV_ERR_UNSUPPORTED with the register and shared-memory figures otherwise), "attn_self_scan" (1 = batches of up to 32 requests run without the
  * prep launch, the kernels scan the lengths themselves, default; 0 = always launch it), "proj_split_k" (0 = automatic), "profile_attn" (0/1, see dkv_profile_read), "wait_limit_ms" (how long
  * dkv_decode_exchange's consumer kernel waits for its peers before it reports DKV_STATUS_WAIT_TIMEOUT; 2000). */

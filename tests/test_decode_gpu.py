@@ -449,8 +449,9 @@ def test_results_do_not_depend_on_scheduling(nh_q, nh_kv, host):
 
 @pytest.mark.parametrize("nh_q,nh_kv", [(4, 4), (8, 2), (16, 1)])
 def test_units_per_warp_floor(nh_q, nh_kv):
-    """Pools in HBM: a floor on the tiles a warp takes (short steps leave fewer partial records).  Every floor, from
-    none to one that leaves a handful of warps with work, gives the oracle's result."""
+    """Pools in HBM: below `attn_min_units` tiles per warp of the grid a step is split the short-step way (about 70 %
+    of the warps, two tiles or more each, dealt out over the CTAs in turn).  Every threshold, from "never" to one that
+    makes every step here a short one, gives the oracle's result."""
     ctx = get_context(0)
     outs = []
     try:
