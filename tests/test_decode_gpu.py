@@ -429,6 +429,25 @@ def test_randomised_configurations(seed):
         ctx.set("proj_decode", -1)
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_matrix_vector_projection_randomised(seed):
+    """Seeded random draws of the shapes the matrix-vector projection takes (one or two requests, hidden size a
+    multiple of 1024, pool in HBM): head counts, groupings, page sizes, lengths, with and without RoPE, every form of
+    the streaming kernel; each compared with the oracle (output, stored rows, untouched slots)."""
+    import random
+
+    rnd = random.Random(7100 + seed)
+    nh_kv = rnd.choice([1, 2, 3, 5, 8])
+    g = rnd.choice([1, 1, 2, 4, 7, 8])
+    hidden = rnd.choice([1024, 2048, 3072, 4096, 7168])
+    page = rnd.choice([1, 4, 16, 64])
+    batch = rnd.choice([1, 1, 2])
+    hi = rnd.choice([1, 40, 700, 5000])
+    lens = [rnd.randint(1, hi) for _ in range(batch)]
+    _run_decode(_shape(hidden, nh_kv * g, nh_kv, rope=rnd.random() < 0.7), lens, page, cfg_id=700 + seed, kv_on_host=False,
+                mode="project", variant=rnd.choice([-1, 0, 1, 2]), mma=rnd.choice([-1, -1, 0, 1]), lid=67)
+
+
 @pytest.mark.parametrize("nh_q,nh_kv,host", [(8, 8, True), (8, 2, False), (8, 2, True), (16, 1, False)])
 def test_results_do_not_depend_on_scheduling(nh_q, nh_kv, host):
     """Static split of the tiles over warps, fixed-order split-K sums and merges: repeated runs give the same bits
